@@ -97,6 +97,19 @@ class Model:
             torch.cuda.empty_cache()
 
 
+DEFAULT_MAX_TOKENS = 65536
+
+
+def _cache_sizes(spec, max_tokens: Optional[int]):
+    """(positions the cache holds in all, the longest sequence it takes).  The default is 8 sequences of
+    the model's full length, at most DEFAULT_MAX_TOKENS; a design without a longest sequence of its own
+    is bounded by the cache."""
+    if max_tokens is None:
+        max_tokens = min(8 * spec.max_positions, DEFAULT_MAX_TOKENS)
+    pages = max(1, -(-int(max_tokens) // 64))
+    return max_tokens, min(spec.max_positions, pages * 64)
+
+
 def build_model(arch: Architecture, config) -> DecoderModel:
     return DecoderModel(arch.build_spec(config))
 
@@ -133,9 +146,8 @@ def load(path: str, dtype="bfloat16", max_tokens: Optional[int] = None, device="
                                       declared=declared, keep_stored=keep_stored)
         model.load(tensors)
         del tensors
-        if max_tokens is None:
-            max_tokens = 8 * model.spec.max_positions
-        cache = SequenceCache(model.cache_requests(), max_tokens, model.spec.max_positions,
+        max_tokens, positions = _cache_sizes(model.spec, max_tokens)
+        cache = SequenceCache(model.cache_requests(), max_tokens, positions,
                               cdt, device, max_slots=max_slots)
         engine = Engine(model, cache, cdt, device)
     info = LoadInfo(path=os.path.abspath(path), architecture=arch.name,
@@ -181,9 +193,8 @@ def load_random(config, seed: int = 0, dtype="bfloat16", max_tokens: Optional[in
             tensors[key] = t.to(device).to(resident_dtype(spec, storage, cdt, storage)).contiguous()
         model.load(tensors)
         del tensors
-        if max_tokens is None:
-            max_tokens = 8 * model.spec.max_positions
-        cache = SequenceCache(model.cache_requests(), max_tokens, model.spec.max_positions,
+        max_tokens, positions = _cache_sizes(model.spec, max_tokens)
+        cache = SequenceCache(model.cache_requests(), max_tokens, positions,
                               cdt, device, max_slots=max_slots)
         engine = Engine(model, cache, cdt, device)
     info = LoadInfo(path=f"random:{seed}", architecture=arch.name,

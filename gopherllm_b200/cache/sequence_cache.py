@@ -34,7 +34,7 @@ RELEASED = -1        # in a sequence's list of pages: this one lay before the wi
 @dataclass
 class KVView:
     """What a mixer gets for its run: this entry's pages of keys and values
-    ([pages, kv_heads, PAGE, head_dim] each), the group whose page table
+    ([pages, kv_heads, PAGE, head_dim] and [pages, kv_heads, PAGE, value_dim]), the group whose page table
     (ctx.pages[group]) addresses them, and whether this run writes them."""
     group: int
     k: torch.Tensor
@@ -55,11 +55,13 @@ class _Group:
         self.gid, self.req = gid, req
         self.entries: List[int] = []
         self.pool = IdPool(n_pages, f"page of cache group {gid}")
-        self.storage: Optional[torch.Tensor] = None
+        self.keys: Optional[torch.Tensor] = None        # [entries, pages, kv_heads, PAGE, head_dim]
+        self.values: Optional[torch.Tensor] = None      # [entries, pages, kv_heads, PAGE, value_dim]
 
 
 class SequenceCache:
-    """requests[i] is what cache entry i needs (KVRequest, StateRequest or None).
+    """requests[i] is what cache entry i needs: KVRequest, StateRequest, None, or a tuple of those for a
+    mixer made of several (its view is then the tuple of their views).
 
     max_tokens: positions all live sequences may hold together, each sequence
     rounded up to a whole page.  max_positions: the longest a sequence may get.
@@ -77,29 +79,41 @@ class SequenceCache:
         self._entry: Dict[int, Tuple[str, int, int]] = {}     # entry -> (kind, group/state index, index in it)
         self._states: List[torch.Tensor] = []
         by_shape: Dict[KVRequest, _Group] = {}
-        for i, req in enumerate(requests):
-            if req is None:
-                continue
+
+        def register(key, req):
             if isinstance(req, KVRequest):
                 g = by_shape.get(req)
                 if g is None:
                     g = _Group(len(self.groups), req, self.n_pages)
                     by_shape[req] = g
                     self.groups.append(g)
-                self._entry[i] = ("kv", g.gid, len(g.entries))
-                g.entries.append(i)
+                self._entry[key] = ("kv", g.gid, len(g.entries))
+                g.entries.append(key)
             elif isinstance(req, StateRequest):
                 rows = (torch.zeros((self.max_slots, *req.shape), dtype=torch.float32, device=device)
                         if allocate else None)
-                self._entry[i] = ("state", len(self._states), 0)
+                self._entry[key] = ("state", len(self._states), 0)
                 self._states.append(rows)
             else:
-                raise TypeError(f"cache entry {i}: unknown request {req!r}")
+                raise TypeError(f"cache entry {key}: unknown request {req!r}")
+
+        for i, req in enumerate(requests):
+            if req is None:
+                continue
+            if isinstance(req, (tuple, list)):
+                self._entry[i] = ("several", len(req), 0)
+                for j, r in enumerate(req):
+                    if r is not None:
+                        register((i, j), r)
+            else:
+                register(i, req)
         if allocate:
             for g in self.groups:
                 r = g.req
-                g.storage = torch.empty((len(g.entries), 2, self.n_pages, r.num_kv_heads, PAGE, r.head_dim),
-                                        dtype=dtype, device=device)
+                g.keys = torch.empty((len(g.entries), self.n_pages, r.num_kv_heads, PAGE, r.head_dim),
+                                     dtype=dtype, device=device)
+                g.values = torch.empty((len(g.entries), self.n_pages, r.num_kv_heads, PAGE, r.value_dim or r.head_dim),
+                                       dtype=dtype, device=device)
         # per-slot bookkeeping
         self._length = [0] * self.max_slots
         self._pages: List[List[List[int]]] = [[[] for _ in self.groups] for _ in range(self.max_slots)]
@@ -108,22 +122,25 @@ class SequenceCache:
 
     # -- sizes ------------------------------------------------------------
     def bytes(self) -> int:
-        n = sum(g.storage.numel() * g.storage.element_size() for g in self.groups if g.storage is not None)
+        n = sum(t.numel() * t.element_size() for g in self.groups for t in (g.keys, g.values) if t is not None)
         return n + sum(s.numel() * 4 for s in self._states if s is not None)
 
     def bytes_per_position(self) -> int:
         """Key and value bytes one cached position occupies, all entries together."""
         es = torch.empty((), dtype=self.dtype).element_size()
-        return sum(len(g.entries) * 2 * g.req.num_kv_heads * g.req.head_dim * es for g in self.groups)
+        return sum(len(g.entries) * g.req.num_kv_heads * (g.req.head_dim + (g.req.value_dim or g.req.head_dim)) * es
+                   for g in self.groups)
 
     # -- views ------------------------------------------------------------
     def view(self, entry: int, writes: bool = True):
         if entry not in self._entry:
             return None
         kind, a, b = self._entry[entry]
+        if kind == "several":
+            return tuple(self.view((entry, j), writes) for j in range(a))
         if kind == "kv":
-            st = self.groups[a].storage
-            return KVView(group=a, k=st[b, 0], v=st[b, 1], writes=writes)
+            g = self.groups[a]
+            return KVView(group=a, k=g.keys[b], v=g.values[b], writes=writes)
         return StateView(rows=self._states[a], writes=writes)
 
     # -- sequences --------------------------------------------------------

@@ -6,10 +6,12 @@ import os
 
 from .registry import (Architecture, architecture_from_config, known_architectures,
                        register_architecture, resolve_architecture)
-from .specs import (BlockSpec, FeedForwardSpec, MixerSpec, ModelSpec, NormSpec,
-                    PositionSpec, ScheduleEntry, default_schedule)
+from .specs import (BlockSpec, FeedForwardSpec, MixerSpec, ModelSpec, NormSpec, PassEntry,
+                    PositionSpec, ScheduleEntry, default_schedule, looped_schedule)
 from . import phi as _phi  # registers the architecture
 from .phi import PhiConfig
+from . import vopedra as _vopedra  # registers the architecture
+from .vopedra import VopedraConfig
 
 
 def read_config_json(folder: str) -> dict:

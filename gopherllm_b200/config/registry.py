@@ -76,13 +76,14 @@ def resolve_architecture(label: str) -> Optional[Architecture]:
 
 def architecture_from_config(cfg: dict) -> Architecture:
     """Pick the architecture a config.json declares: ``architectures[0]``
-    first, then ``model_type``."""
+    first, then ``model_type``, then a plain ``architecture`` string."""
     declared = []
     archs = cfg.get("architectures")
     if isinstance(archs, (list, tuple)):
         declared += [a for a in archs if isinstance(a, str)]
-    if isinstance(cfg.get("model_type"), str):
-        declared.append(cfg["model_type"])
+    for key in ("model_type", "architecture"):
+        if isinstance(cfg.get(key), str):
+            declared.append(cfg[key])
     for label in declared:
         arch = resolve_architecture(label)
         if arch is not None:

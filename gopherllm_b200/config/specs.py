@@ -52,12 +52,15 @@ class PositionSpec:
 class MixerSpec:
     """Token mixer of a block.  kind "attention" is softmax attention over a
     key/value cache with ``num_kv_heads`` groups; ``window`` 0 means all keys,
-    w > 0 means the last w keys (the query's own position included)."""
+    w > 0 means the last w keys (the query's own position included).  Other kinds (mixers that keep a
+    state instead of a cache, a pair of mixers side by side) read the sizes they share with attention
+    from the same fields and their own constants from ``extra``."""
     kind: str
     hidden: int
     num_heads: int = 0
     num_kv_heads: int = 0
     head_dim: int = 0
+    value_dim: int = 0            # size of a head's values where it differs from head_dim (0: the same)
     window: int = 0
     q_scale: float = 1.0          # multiplies q after position encoding
     bias: bool = True
@@ -92,7 +95,7 @@ class BlockSpec:
     arrangement: str
     norm: NormSpec
     mixer: MixerSpec
-    ffn: FeedForwardSpec
+    ffn: Optional[FeedForwardSpec]           # None: a layer without a feed-forward (arrangements that allow it)
     norm2: Optional[NormSpec] = None
     extra: Tuple[Tuple[str, object], ...] = ()   # free-form options for other arrangements (further norms, branches)
 
@@ -101,13 +104,24 @@ class BlockSpec:
 
 
 @dataclass(frozen=True)
+class PassEntry:
+    """What happens to the residual stream right before a run that opens a pass over a looped range of
+    layers: the stream as it left the embedding is added (``add_embedding``), then row ``index`` of the
+    model's table of per-pass vectors (``ModelSpec.pass_vectors`` rows)."""
+    index: int
+    add_embedding: bool = False
+
+
+@dataclass(frozen=True)
 class ScheduleEntry:
     """One run of a layer.  ``layer`` indexes ModelSpec.layers; ``cache`` is
     the cache entry this run reads (None: the mixer keeps nothing);
-    ``writes`` False lets a run read an entry another run filled."""
+    ``writes`` False lets a run read an entry another run filled; ``enter``
+    marks the first run of a pass over a looped range."""
     layer: int
     cache: Optional[int]
     writes: bool = True
+    enter: Optional[PassEntry] = None
 
 
 @dataclass(frozen=True)
@@ -128,6 +142,10 @@ class ModelSpec:
     # logits * logit_scale, then softcap * tanh(logits / softcap) when softcap > 0 (model.go:2555-2564)
     logit_scale: float = 1.0
     logit_softcap: float = 0.0
+    # a norm between the embedding and the first layer; its output is "the embedding's output"
+    embedding_norm: Optional[NormSpec] = None
+    # rows of the table of learned vectors added at the start of each pass over a looped range; 0: none
+    pass_vectors: int = 0
 
     def __post_init__(self):
         if self.position_table and self.position_table < self.max_positions:
@@ -138,6 +156,9 @@ class ModelSpec:
         for e in self.schedule:
             if not 0 <= e.layer < len(self.layers):
                 raise ValueError(f"schedule names layer {e.layer}, model has {len(self.layers)}")
+        for e in self.schedule:
+            if e.enter is not None and not 0 <= e.enter.index < max(self.pass_vectors, 1):
+                raise ValueError(f"a run enters pass {e.enter.index}, the model has {self.pass_vectors} pass vectors")
         writers = {}
         for e in self.schedule:
             if e.cache is None:
@@ -159,3 +180,22 @@ class ModelSpec:
 def default_schedule(num_layers: int) -> Tuple[ScheduleEntry, ...]:
     """Layer i runs once, in order, on cache entry i."""
     return tuple(ScheduleEntry(layer=i, cache=i) for i in range(num_layers))
+
+
+def looped_schedule(num_layers: int, start: int, stop: int, times: int) -> Tuple[ScheduleEntry, ...]:
+    """Layers 0..start-1 once, then layers start..stop-1 ``times`` times in a row with the same weights,
+    then the rest once.  Every run has a cache entry of its own (a pass never sees another pass's keys or
+    state).  The first run of each pass is marked: pass t adds the model's pass vector t, and every pass
+    but the first adds the embedding's output before that."""
+    if not (0 <= start <= stop <= num_layers) or times < 1:
+        raise ValueError(f"loop over layers {start}..{stop} x {times} does not fit {num_layers} layers")
+    runs = []
+    for i in range(start):
+        runs.append(ScheduleEntry(layer=i, cache=len(runs)))
+    for t in range(times):
+        for i in range(start, stop):
+            enter = PassEntry(index=t, add_embedding=t > 0) if i == start else None
+            runs.append(ScheduleEntry(layer=i, cache=len(runs), enter=enter))
+    for i in range(stop, num_layers):
+        runs.append(ScheduleEntry(layer=i, cache=len(runs)))
+    return tuple(runs)

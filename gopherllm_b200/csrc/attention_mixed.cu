@@ -1,0 +1,292 @@
+// Softmax attention over the paged cache whose heads' weights are mixed before they meet the
+// values, with keys and values of different sizes; 32-bit arithmetic, any sizes, both element types.
+//
+// With weights p_g(i, j) = softmax_j(q_g(i) . k(j)) of query head g, head h of the mixer applies
+//     w_h(i, j) = sum_g M[h, g] p_g(i, j)
+// to the values of its own key/value head c(h).  The sum over j is linear, so
+//     out_h(i) = sum_g M[h, g] * A[g, c(h)](i),     A[g, c](i) = sum_j p_g(i, j) v_c(j):
+// the first kernel computes A for every pair (query head, value head) with a running maximum and
+// sum (a pair's scores come from the query head's own key head), the second mixes.  Without a table
+// the pairs are (g, c(g)) alone and the second kernel only converts.  A query at position p sees keys
+// lo..p, lo = 0 or p-window+1.
+#include "common.cuh"
+
+struct MixedAttnArgs {
+    const void* q;            // [T, nH*hd] activation type, already scaled
+    float* pairs;             // [T, nH, nVal, vd] 32-bit; nVal = nKV with a table, 1 without
+    void* out;                // [T, nH*vd] activation type
+    const void* k_cache;      // [pages, nKV, GL_PAGE, hd] cache type
+    const void* v_cache;      // [pages, nKV, GL_PAGE, vd] cache type
+    const float* mix;         // [nH, nH] or null
+    const int* seq_qstart;
+    const int* seq_qlen;
+    const int* seq_ctx;
+    const int* pages;         // [B, max_pages]
+    int T, B, nH, nKV, hd, vd, max_pages, window, max_qlen;
+    int n_pages;
+};
+
+#define AM_ROWS 8
+
+// Prompts: one warp owns one query row of one pair; the warps of a block are consecutive tokens of a
+// sequence and share the key and value tiles staged in shared memory.
+template <typename TA, typename TC, int NACC>
+__global__ void __launch_bounds__(AM_ROWS * 32)
+attn_pairs_kernel(MixedAttnArgs a) {
+    extern __shared__ float smem[];
+    gl_grid_launch_dependents();
+    gl_grid_wait();
+    const int hd = a.hd, vd = a.vd, ks = hd + 1;
+    float* Ks = smem;                       // [GL_PAGE][hd+1]
+    float* Vs = Ks + GL_PAGE * ks;          // [GL_PAGE][vd]
+    float* Qs = Vs + GL_PAGE * vd;          // [AM_ROWS][hd]
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int b = blockIdx.z;
+    const int nVal = a.mix ? a.nKV : 1;
+    const int g = blockIdx.y / nVal;                              // query head
+    const int kh = g / (a.nH / a.nKV);                            // its key head
+    const int vh = a.mix ? blockIdx.y - g * nVal : kh;            // the pair's value head
+    const int qlen = a.seq_qlen[b];
+    const int row0 = blockIdx.x * AM_ROWS;
+    if (row0 >= qlen) return;
+    const int ctx = a.seq_ctx[b];
+    const int total = ctx + qlen;
+    const int idx = row0 + warp;
+    const bool live = idx < qlen;
+    const int p = ctx + idx;
+    const int lo = (a.window > 0 && p - a.window + 1 > 0) ? p - a.window + 1 : 0;
+    const int rows_here = min(AM_ROWS, qlen - row0);
+    const int p_first = ctx + row0, p_last = ctx + row0 + rows_here - 1;
+    const int lo_cta = (a.window > 0 && p_first - a.window + 1 > 0) ? p_first - a.window + 1 : 0;
+
+    float* qv = Qs + warp * hd;
+    if (live) {
+        const TA* qsrc = (const TA*)a.q + ((size_t)(a.seq_qstart[b] + idx) * a.nH + g) * hd;
+        for (int d = lane; d < hd; d += 32) qv[d] = gl_load(qsrc + d);
+    }
+    float acc[NACC];
+#pragma unroll
+    for (int i = 0; i < NACC; ++i) acc[i] = 0.f;
+    float m = -INFINITY, l = 0.f;
+
+    const int* pg = a.pages + (size_t)b * a.max_pages;
+    for (int page_i = lo_cta / GL_PAGE; page_i <= p_last / GL_PAGE; ++page_i) {
+        const int page = gl_checked(pg[gl_checked(page_i, a.max_pages, GL_BAD_POSITION)], a.n_pages > 0 ? a.n_pages : 0x7fffffff, GL_BAD_PAGE);
+        const TC* kp = (const TC*)a.k_cache + ((size_t)page * a.nKV + kh) * GL_PAGE * hd;
+        const TC* vp = (const TC*)a.v_cache + ((size_t)page * a.nKV + vh) * GL_PAGE * vd;
+        const int j0 = page_i * GL_PAGE;
+        __syncthreads();
+        for (int e = threadIdx.x; e < GL_PAGE * hd; e += blockDim.x) {
+            const int r = e / hd, d = e - r * hd;
+            Ks[r * ks + d] = j0 + r < total ? gl_load(kp + e) : 0.f;      // rows past the sequence were never written
+        }
+        for (int e = threadIdx.x; e < GL_PAGE * vd; e += blockDim.x)
+            Vs[e] = j0 + e / vd < total ? gl_load(vp + e) : 0.f;
+        __syncthreads();
+        if (!live) continue;
+#pragma unroll 1
+        for (int half = 0; half < GL_PAGE / 32; ++half) {
+            const int jj = half * 32 + lane, j = j0 + jj;
+            const bool ok = j >= lo && j <= p;
+            float s = -INFINITY;
+            if (ok) {
+                const float* kr = Ks + jj * ks;
+                float d0 = 0.f;
+                for (int d = 0; d < hd; ++d) d0 = fmaf(qv[d], kr[d], d0);
+                s = d0;
+            }
+            const float m_new = fmaxf(m, gl_warp_max(s));
+            if (m_new == -INFINITY) continue;
+            const float pj = ok ? expf(s - m_new) : 0.f;
+            const float corr = expf(m - m_new);
+            l = l * corr + gl_warp_sum(pj);
+            m = m_new;
+#pragma unroll
+            for (int i = 0; i < NACC; ++i) acc[i] *= corr;
+            const float* vr = Vs + half * 32 * vd;
+            for (int k = 0; k < 32; ++k) {
+                const float pk = __shfl_sync(0xffffffffu, pj, k);
+#pragma unroll
+                for (int i = 0; i < NACC; ++i) {
+                    const int d = lane + 32 * i;
+                    if (d < vd) acc[i] = fmaf(pk, vr[k * vd + d], acc[i]);
+                }
+            }
+        }
+    }
+    if (!live) return;
+    const float inv = l > 0.f ? 1.0f / l : 0.f;
+    float* o = a.pairs + (((size_t)(a.seq_qstart[b] + idx) * a.nH + g) * nVal + (a.mix ? vh : 0)) * vd;
+#pragma unroll
+    for (int i = 0; i < NACC; ++i) {
+        const int d = lane + 32 * i;
+        if (d < vd) o[d] = acc[i] * inv;
+    }
+}
+
+// One token a sequence: a block owns one pair of one sequence, its warps take the pages of the
+// context in turn straight from the cache (a lane a key for the scores, a lane a column for the
+// values) and their partial results are merged in shared memory in warp order.
+#define AM_DWARPS 8
+
+template <typename TA, typename TC, int NACC>
+__global__ void __launch_bounds__(AM_DWARPS * 32)
+attn_pairs_decode_kernel(MixedAttnArgs a) {
+    extern __shared__ float smem[];
+    gl_grid_launch_dependents();
+    gl_grid_wait();
+    const int hd = a.hd, vd = a.vd;
+    float* qv = smem;                                   // [hd]
+    float* part = qv + hd;                              // [AM_DWARPS][vd + 2]
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int b = blockIdx.y;
+    const int nVal = a.mix ? a.nKV : 1;
+    const int g = blockIdx.x / nVal;
+    const int kh = g / (a.nH / a.nKV);
+    const int vh = a.mix ? blockIdx.x - g * nVal : kh;
+    const int p = a.seq_ctx[b];                         // the token's position; keys lo..p
+    const int lo = (a.window > 0 && p - a.window + 1 > 0) ? p - a.window + 1 : 0;
+    const int row = a.seq_qstart[b];
+    const TA* qsrc = (const TA*)a.q + ((size_t)row * a.nH + g) * hd;
+    for (int d = threadIdx.x; d < hd; d += blockDim.x) qv[d] = gl_load(qsrc + d);
+    __syncthreads();
+    float acc[NACC];
+#pragma unroll
+    for (int i = 0; i < NACC; ++i) acc[i] = 0.f;
+    float m = -INFINITY, l = 0.f;
+    const int* pg = a.pages + (size_t)b * a.max_pages;
+    for (int page_i = lo / GL_PAGE + warp; page_i <= p / GL_PAGE; page_i += AM_DWARPS) {
+        const int page = gl_checked(pg[gl_checked(page_i, a.max_pages, GL_BAD_POSITION)], a.n_pages > 0 ? a.n_pages : 0x7fffffff, GL_BAD_PAGE);
+        const TC* kp = (const TC*)a.k_cache + ((size_t)page * a.nKV + kh) * GL_PAGE * hd;
+        const TC* vp = (const TC*)a.v_cache + ((size_t)page * a.nKV + vh) * GL_PAGE * vd;
+        const int j0 = page_i * GL_PAGE;
+#pragma unroll 1
+        for (int half = 0; half < GL_PAGE / 32; ++half) {
+            const int jj = half * 32 + lane, j = j0 + jj;
+            const bool ok = j >= lo && j <= p;
+            float s = -INFINITY;
+            if (ok) {
+                const TC* kr = kp + (size_t)jj * hd;
+                float d0 = 0.f;
+                for (int d = 0; d < hd; ++d) d0 = fmaf(qv[d], gl_load(kr + d), d0);
+                s = d0;
+            }
+            const float m_new = fmaxf(m, gl_warp_max(s));
+            if (m_new == -INFINITY) continue;
+            const float pj = ok ? expf(s - m_new) : 0.f;
+            const float corr = expf(m - m_new);
+            l = l * corr + gl_warp_sum(pj);
+            m = m_new;
+#pragma unroll
+            for (int i = 0; i < NACC; ++i) acc[i] *= corr;
+            const TC* vr = vp + (size_t)half * 32 * vd;
+            // keys past p were never written, keys before lo may lie in a page that was given back
+            const int kmin = max(0, lo - (j0 + half * 32)), kmax = min(32, p - (j0 + half * 32) + 1);
+            for (int k = kmin; k < kmax; ++k) {
+                const float pk = __shfl_sync(0xffffffffu, pj, k);
+#pragma unroll
+                for (int i = 0; i < NACC; ++i) {
+                    const int d = lane + 32 * i;
+                    if (d < vd) acc[i] = fmaf(pk, gl_load(vr + (size_t)k * vd + d), acc[i]);
+                }
+            }
+        }
+    }
+    float* mine = part + warp * (vd + 2);
+#pragma unroll
+    for (int i = 0; i < NACC; ++i) {
+        const int d = lane + 32 * i;
+        if (d < vd) mine[d] = acc[i];
+    }
+    if (lane == 0) { mine[vd] = m; mine[vd + 1] = l; }
+    __syncthreads();
+    float mm = -INFINITY;
+    for (int w = 0; w < AM_DWARPS; ++w) mm = fmaxf(mm, part[w * (vd + 2) + vd]);
+    float ll = 0.f;
+    for (int w = 0; w < AM_DWARPS; ++w) {
+        const float mw = part[w * (vd + 2) + vd];
+        if (mw > -INFINITY) ll += part[w * (vd + 2) + vd + 1] * expf(mw - mm);
+    }
+    const float inv = ll > 0.f ? 1.0f / ll : 0.f;
+    float* o = a.pairs + (((size_t)row * a.nH + g) * nVal + (a.mix ? vh : 0)) * vd;
+    for (int d = threadIdx.x; d < vd; d += blockDim.x) {
+        float s = 0.f;
+        for (int w = 0; w < AM_DWARPS; ++w) {
+            const float mw = part[w * (vd + 2) + vd];
+            if (mw > -INFINITY) s = fmaf(part[w * (vd + 2) + d], expf(mw - mm), s);
+        }
+        o[d] = s * inv;
+    }
+}
+
+// out[t, h, :] = sum_g M[h, g] pairs[t, g, c(h), :]   (without a table: pairs[t, h, 0, :])
+template <typename TA>
+__global__ void __launch_bounds__(256)
+head_mix_kernel(MixedAttnArgs a) {
+    gl_grid_launch_dependents();
+    gl_grid_wait();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const long long n = (long long)a.T * a.nH * a.vd;
+    if (i >= n) return;
+    const int d = (int)(i % a.vd);
+    const int h = (int)((i / a.vd) % a.nH);
+    const long long t = i / ((long long)a.vd * a.nH);
+    float y;
+    if (a.mix) {
+        const int c = h / (a.nH / a.nKV);
+        y = 0.f;
+        for (int g = 0; g < a.nH; ++g)
+            y = fmaf(a.mix[h * a.nH + g], a.pairs[(((size_t)t * a.nH + g) * a.nKV + c) * a.vd + d], y);
+    } else {
+        y = a.pairs[((size_t)t * a.nH + h) * a.vd + d];
+    }
+    gl_store((TA*)a.out + i, y);
+}
+
+template <typename TA, typename TC, int NACC>
+static int launch_mixed(const MixedAttnArgs& a, cudaStream_t stream) {
+    const int pairs = a.nH * (a.mix ? a.nKV : 1);
+    int rc;
+    if (a.max_qlen == 1) {
+        const size_t smem = ((size_t)a.hd + (size_t)AM_DWARPS * (a.vd + 2)) * sizeof(float);
+        rc = gl_launch(attn_pairs_decode_kernel<TA, TC, NACC>, dim3(pairs, a.B), dim3(AM_DWARPS * 32), smem, stream, 1, a);
+    } else {
+        const size_t smem = ((size_t)GL_PAGE * (a.hd + 1) + (size_t)GL_PAGE * a.vd + (size_t)AM_ROWS * a.hd) * sizeof(float);
+        auto kern = attn_pairs_kernel<TA, TC, NACC>;
+        if (smem > 48 * 1024) {
+            if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
+                cudaGetLastError();
+                return GL_ERR_SMEM;
+            }
+        }
+        rc = gl_launch(kern, dim3((a.max_qlen + AM_ROWS - 1) / AM_ROWS, pairs, a.B), dim3(AM_ROWS * 32), smem, stream, 1, a);
+    }
+    if (rc != 0) return rc;
+    const long long n = (long long)a.T * a.nH * a.vd;
+    return gl_launch(head_mix_kernel<TA>, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, 1, a);
+}
+
+template <typename TA, typename TC>
+static int dispatch_mixed(const MixedAttnArgs& a, cudaStream_t stream) {
+    switch ((a.vd + 31) / 32) {
+        case 1: return launch_mixed<TA, TC, 1>(a, stream);
+        case 2: return launch_mixed<TA, TC, 2>(a, stream);
+        case 3: return launch_mixed<TA, TC, 3>(a, stream);
+        case 4: return launch_mixed<TA, TC, 4>(a, stream);
+        case 5: return launch_mixed<TA, TC, 5>(a, stream);
+        case 6: return launch_mixed<TA, TC, 6>(a, stream);
+        case 7: return launch_mixed<TA, TC, 7>(a, stream);
+        case 8: return launch_mixed<TA, TC, 8>(a, stream);
+        default: return GL_ERR_SHAPE;
+    }
+}
+
+GL_API int gl_attention_mixed(const MixedAttnArgs* args, int act_dtype, int cache_dtype, cudaStream_t stream) {
+    const MixedAttnArgs& a = *args;
+    if (a.B <= 0 || a.max_qlen <= 0 || a.T <= 0) return GL_OK;
+    if (a.hd <= 0 || a.hd > 256 || a.vd <= 0 || a.vd > 256 || a.nH <= 0 || a.nKV <= 0 || a.nH % a.nKV) return GL_ERR_SHAPE;
+    if (a.B > 65535 || a.nH * a.nKV > 65535) return GL_ERR_SHAPE;
+    if (act_dtype == GL_F32 && cache_dtype == GL_F32) return dispatch_mixed<float, float>(a, stream);
+    if (act_dtype == GL_BF16 && cache_dtype == GL_BF16) return dispatch_mixed<__nv_bfloat16, __nv_bfloat16>(a, stream);
+    return GL_ERR_DTYPE;
+}

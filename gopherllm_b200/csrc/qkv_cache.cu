@@ -204,3 +204,111 @@ GL_API int gl_qkv_cache(const QkvCacheArgs* args, int act_dtype, int cache_dtype
     if (act_dtype == GL_F32 && cache_dtype == GL_BF16) return gl_launch(qkv_cache_kernel<float, __nv_bfloat16>, g, b, smem, stream, 1, a);
     return GL_ERR_DTYPE;
 }
+
+// ---------------------------------------------------------------------------
+// The same step for a mixer that normalises queries and keys over the WHOLE projection (all heads of a
+// token at once, root mean square, one weight per column) before the rotation, and whose values may
+// have another size than its keys:
+//   q <- q / sqrt(mean(q^2) + eps) * gq over nH*hd columns, k likewise over nKV*hd; rotation of the
+//   first 2*half dims of every head; q * q_scale to q_out; k and v into the token's cache row.
+// One block per token; statistics, rotation and scale in 32-bit.
+// ---------------------------------------------------------------------------
+struct QkvRowNormArgs {
+    const void* qkv;          // [T, ld] activation type: q (nH*hd), k (nKV*hd), v (nKV*vd) from column 0 on
+    void* q_out;              // [T, nH*hd] activation type
+    void* k_cache;            // [pages, nKV, GL_PAGE, hd] cache type
+    void* v_cache;            // [pages, nKV, GL_PAGE, vd] cache type
+    const float* cosv;        // [T, half] or null
+    const float* sinv;
+    const float* q_gamma;     // [nH*hd] or null (no norm)
+    const float* k_gamma;     // [nKV*hd] or null
+    const int* tok_seq;
+    const int* tok_pos;
+    const int* pages;         // [B, max_pages]
+    int T, ld, nH, nKV, hd, vd, half, max_pages, interleaved, write_kv;
+    float eps, q_scale;
+    int n_pages;
+};
+
+template <typename TA, typename TC>
+__global__ void __launch_bounds__(128)
+qkv_rownorm_cache_kernel(QkvRowNormArgs a) {
+    extern __shared__ float smem[];
+    __shared__ float red[4];
+    gl_grid_launch_dependents();
+    gl_grid_wait();
+    const int t = blockIdx.x;
+    const int nq = a.nH * a.hd, nk = a.nKV * a.hd, nv = a.nKV * a.vd;
+    const TA* row = (const TA*)a.qkv + (size_t)t * a.ld;
+    float* v = smem;                                  // q then k, 32-bit
+    float sq = 0.f, sk = 0.f;
+    for (int i = threadIdx.x; i < nq + nk; i += blockDim.x) {
+        const float x = gl_load(row + i);
+        v[i] = x;
+        if (i < nq) sq += x * x; else sk += x * x;
+    }
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    float inv_q = 1.f, inv_k = 1.f;
+    {
+        sq = gl_warp_sum(sq);
+        if (lane == 0) red[w] = sq;
+        __syncthreads();
+        const float tq = (red[0] + red[1]) + (red[2] + red[3]);
+        __syncthreads();
+        sk = gl_warp_sum(sk);
+        if (lane == 0) red[w] = sk;
+        __syncthreads();
+        const float tk = (red[0] + red[1]) + (red[2] + red[3]);
+        if (a.q_gamma) inv_q = 1.0f / sqrtf(tq / (float)nq + a.eps);
+        if (a.k_gamma) inv_k = 1.0f / sqrtf(tk / (float)nk + a.eps);
+    }
+    for (int i = threadIdx.x; i < nq + nk; i += blockDim.x) {
+        if (i < nq) { if (a.q_gamma) v[i] = v[i] * inv_q * a.q_gamma[i]; }
+        else if (a.k_gamma) v[i] = v[i] * inv_k * a.k_gamma[i - nq];
+    }
+    __syncthreads();
+    if (a.half > 0 && a.cosv) {
+        const float* cs = a.cosv + (size_t)t * a.half;
+        const float* sn = a.sinv + (size_t)t * a.half;
+        const int pairs = (a.nH + a.nKV) * a.half;
+        for (int e = threadIdx.x; e < pairs; e += blockDim.x) {
+            const int head = e / a.half, i = e - head * a.half;
+            float* hv = v + (size_t)head * a.hd;
+            const int i0 = a.interleaved ? 2 * i : i;
+            const int i1 = a.interleaved ? 2 * i + 1 : i + a.half;
+            const float c = cs[i], s = sn[i];
+            const float u = hv[i0], x = hv[i1];
+            hv[i0] = u * c - x * s;
+            hv[i1] = x * c + u * s;
+        }
+        __syncthreads();
+    }
+    TA* qo = (TA*)a.q_out + (size_t)t * nq;
+    for (int i = threadIdx.x; i < nq; i += blockDim.x) gl_store(qo + i, v[i] * a.q_scale);
+    if (!a.write_kv) return;
+    const int pos = a.tok_pos[t];
+    const int slot = gl_checked(pos / GL_PAGE, a.max_pages, GL_BAD_POSITION);
+    const int page = gl_checked(a.pages[(size_t)a.tok_seq[t] * a.max_pages + slot], a.n_pages > 0 ? a.n_pages : 0x7fffffff, GL_BAD_PAGE);
+    for (int i = threadIdx.x; i < nk; i += blockDim.x) {
+        const int head = i / a.hd, d = i - head * a.hd;
+        gl_store((TC*)a.k_cache + (((size_t)page * a.nKV + head) * GL_PAGE + (pos % GL_PAGE)) * a.hd + d, v[nq + i]);
+    }
+    for (int i = threadIdx.x; i < nv; i += blockDim.x) {
+        const int head = i / a.vd, d = i - head * a.vd;
+        gl_store((TC*)a.v_cache + (((size_t)page * a.nKV + head) * GL_PAGE + (pos % GL_PAGE)) * a.vd + d,
+                 gl_load(row + nq + nk + i));
+    }
+}
+
+GL_API int gl_qkv_rownorm_cache(const QkvRowNormArgs* args, int act_dtype, int cache_dtype, cudaStream_t stream) {
+    const QkvRowNormArgs& a = *args;
+    if (a.T <= 0) return GL_OK;
+    if (a.hd <= 0 || a.vd <= 0 || a.nH <= 0 || a.nKV <= 0 || 2 * a.half > a.hd) return GL_ERR_SHAPE;
+    const size_t smem = (size_t)(a.nH + a.nKV) * a.hd * sizeof(float);
+    if (smem > 48 * 1024) return GL_ERR_SMEM;
+    const dim3 g((unsigned)a.T), b(128);
+    if (act_dtype == GL_F32 && cache_dtype == GL_F32) return gl_launch(qkv_rownorm_cache_kernel<float, float>, g, b, smem, stream, 1, a);
+    if (act_dtype == GL_BF16 && cache_dtype == GL_BF16)
+        return gl_launch(qkv_rownorm_cache_kernel<__nv_bfloat16, __nv_bfloat16>, g, b, smem, stream, 1, a);
+    return GL_ERR_DTYPE;
+}

@@ -1,0 +1,451 @@
+// Mixers that carry a fixed-size state from token to token instead of a growing cache:
+// matrix memories with outer-product updates (an exponentially gated one with a normaliser and a
+// running maximum, and one whose per-channel forget gate also sets what is written) and a
+// selective state-space scan behind a short causal convolution.
+//
+// A step brings, for every sequence of the batch, a run of one or more tokens; the state of a
+// sequence lives in its row of a 32-bit table (row = the sequence's slot), is read when the run
+// starts and written back when it ends, so a prompt gives the same result whole, in pieces or token
+// by token.  Everything that enters a recurrence (gates, decays, step sizes, the state itself) is
+// 32-bit; the projections that feed it arrive in the activation type.
+//
+// The scans walk a run's tokens in order.  Work is spread over what is independent: sequences,
+// heads and the columns of a memory (or the channels of the scan); a thread keeps its part of the
+// state in registers for the whole run, and the tokens' inputs are staged in shared memory a few
+// tokens at a time.
+#include "common.cuh"
+
+#define RC_THREADS 128
+#define RC_CHUNK 8          // tokens staged at a time
+
+__device__ __forceinline__ float rc_sigmoid(float x) { return 1.0f / (1.0f + expf(-x)); }
+__device__ __forceinline__ float rc_silu(float x) { return x / (1.0f + expf(-x)); }
+__device__ __forceinline__ float rc_log_sigmoid(float x) { return fminf(x, 0.0f) - log1pf(expf(-fabsf(x))); }
+__device__ __forceinline__ float rc_softplus(float x) { return x > 20.0f ? x : log1pf(expf(x)); }
+
+// ---------------------------------------------------------------------------
+// Matrix memories.  Per head a state S [D, V]; a token's output is S^T q.
+//   kind 0, gated with a normaliser: log gates gi = cap tanh(i/cap), gf = logsigmoid(cap tanh(f/cap));
+//       m' = max(gf + m, gi);  S' = e^(gf+m-m') S + e^(gi-m') k v^T;  n' likewise with k alone;
+//       o = S'^T q / (max(|n'.q|, e^(-m')) + 1e-6).     m starts at 0 (a zeroed state row).
+//   kind 1, forget gate with a lower bound: f = l + (1-l) sigmoid(fpre) per row;
+//       S' = diag(f) S + (1-f) v^T;  o = S'^T q,  q = silu(qpre).
+// State row: S [H, D, V], then for kind 0 n [H, tiles, D] and m [H, tiles], tiles = the blocks of columns a
+// head is spread over (gl_memory_scan_tiles).
+// ---------------------------------------------------------------------------
+struct MemoryScanArgs {
+    const void* proj;         // [T, ld] activation type: the joined projections of the step's tokens
+    float* out;               // [T, H*V] 32-bit
+    float* state;             // [slots, state_stride]
+    const float* lower;       // kind 1: [H*D] lower bounds of the forget gate
+    const int* seq_slot;      // [B]
+    const int* seq_qstart;    // [B]
+    const int* seq_qlen;      // [B]
+    int ld, q_off, k_off, v_off, i_off, f_off;
+    int B, H, D, V, state_stride, kind;
+    float cap, q_scale;
+};
+
+template <typename TA, int DPT, int KIND>
+__global__ void __launch_bounds__(RC_THREADS)
+memory_scan_kernel(MemoryScanArgs a, int R) {
+    extern __shared__ float smem[];
+    gl_grid_launch_dependents();
+    gl_grid_wait();
+    const int D = a.D, V = a.V, H = a.H;
+    const int CT = RC_THREADS / R;                    // columns of a block
+    const int b = blockIdx.z, h = blockIdx.y, col0 = blockIdx.x * CT;
+    const int r = threadIdx.x % R, c = threadIdx.x / R;
+    const int col = col0 + c;
+    const bool live = col < V;
+    const int qlen = a.seq_qlen[b], qstart = a.seq_qstart[b];
+    float* qs = smem;                                 // [CHUNK][D]
+    float* ks = qs + RC_CHUNK * D;                    // [CHUNK][D]   kind 0: k;  kind 1: f
+    float* vs = ks + RC_CHUNK * D;                    // [CHUNK][CT]
+    float* gs = vs + RC_CHUNK * CT;                   // [CHUNK][4]   kind 0: gi, gf, then keep, take; [.][3] reused
+    float* es = gs + RC_CHUNK * 4;                    // [CHUNK]      kind 0: e^(-m')
+
+    float* srow = a.state + (size_t)a.seq_slot[b] * a.state_stride;
+    float* S_g = srow + (size_t)h * D * V;
+    // every block of columns keeps its own copy of the head's normaliser and maximum: a block may start
+    // after another of the same head has finished and written its state back
+    const int tiles = gridDim.x;
+    float* n_g = srow + (size_t)H * D * V + ((size_t)h * tiles + blockIdx.x) * D;
+    float* m_g = srow + (size_t)H * D * V + (size_t)H * tiles * D + (size_t)h * tiles + blockIdx.x;
+    float S[DPT], n[DPT];
+#pragma unroll
+    for (int i = 0; i < DPT; ++i) {
+        const int d = r + R * i;
+        S[i] = (live && d < D) ? S_g[(size_t)d * V + col] : 0.f;
+        n[i] = (KIND == 0 && d < D) ? n_g[d] : 0.f;
+    }
+    float m = KIND == 0 ? *m_g : 0.f;                 // only thread 0 keeps it current
+
+    for (int s0 = 0; s0 < qlen; s0 += RC_CHUNK) {
+        const int ns = min(RC_CHUNK, qlen - s0);
+        __syncthreads();
+        for (int e = threadIdx.x; e < ns * D; e += RC_THREADS) {
+            const int s = e / D, d = e - s * D;
+            const TA* row = (const TA*)a.proj + (size_t)(qstart + s0 + s) * a.ld;
+            const float qp = gl_load(row + a.q_off + h * D + d);
+            if (KIND == 0) {
+                qs[e] = qp * a.q_scale;
+                ks[e] = gl_load(row + a.k_off + h * D + d);
+            } else {
+                qs[e] = rc_silu(qp);
+                const float l = a.lower[h * D + d];
+                ks[e] = l + (1.0f - l) * rc_sigmoid(gl_load(row + a.f_off + h * D + d));
+            }
+        }
+        for (int e = threadIdx.x; e < ns * CT; e += RC_THREADS) {
+            const int s = e / CT, j = e - s * CT;
+            const TA* row = (const TA*)a.proj + (size_t)(qstart + s0 + s) * a.ld;
+            vs[e] = col0 + j < V ? gl_load(row + a.v_off + h * V + col0 + j) : 0.f;
+        }
+        if (KIND == 0) {
+            if (threadIdx.x < ns) {
+                const TA* row = (const TA*)a.proj + (size_t)(qstart + s0 + threadIdx.x) * a.ld;
+                gs[threadIdx.x * 4 + 0] = a.cap * tanhf(gl_load(row + a.i_off + h) / a.cap);
+                gs[threadIdx.x * 4 + 1] = rc_log_sigmoid(a.cap * tanhf(gl_load(row + a.f_off + h) / a.cap));
+            }
+            __syncthreads();
+            if (threadIdx.x == 0) {
+                for (int s = 0; s < ns; ++s) {
+                    const float gi = gs[s * 4 + 0], gf = gs[s * 4 + 1];
+                    const float m_new = fmaxf(gf + m, gi);
+                    gs[s * 4 + 2] = expf(gf + m - m_new);
+                    gs[s * 4 + 3] = expf(gi - m_new);
+                    es[s] = expf(-m_new);
+                    m = m_new;
+                }
+            }
+        }
+        __syncthreads();
+        for (int s = 0; s < ns; ++s) {
+            const float* q = qs + s * D;
+            const float* k = ks + s * D;
+            const float v = vs[s * CT + c];
+            float num = 0.f, nq = 0.f;
+            if (KIND == 0) {
+                const float keep = gs[s * 4 + 2], take = gs[s * 4 + 3];
+#pragma unroll
+                for (int i = 0; i < DPT; ++i) {
+                    const int d = r + R * i;
+                    if (d < D) {
+                        const float kk = take * k[d];
+                        S[i] = fmaf(keep, S[i], kk * v);
+                        n[i] = fmaf(keep, n[i], kk);
+                        num = fmaf(S[i], q[d], num);
+                        nq = fmaf(n[i], q[d], nq);
+                    }
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < DPT; ++i) {
+                    const int d = r + R * i;
+                    if (d < D) {
+                        const float f = k[d];
+                        S[i] = fmaf(f, S[i], (1.0f - f) * v);
+                        num = fmaf(S[i], q[d], num);
+                    }
+                }
+            }
+            for (int o = R >> 1; o > 0; o >>= 1) {
+                num += __shfl_xor_sync(0xffffffffu, num, o);
+                if (KIND == 0) nq += __shfl_xor_sync(0xffffffffu, nq, o);
+            }
+            if (r == 0 && live) {
+                float o = num;
+                if (KIND == 0) o = num / (fmaxf(fabsf(nq), es[s]) + 1e-6f);
+                a.out[(size_t)(qstart + s0 + s) * H * V + (size_t)h * V + col] = o;
+            }
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < DPT; ++i) {
+        const int d = r + R * i;
+        if (d < D) {
+            if (live) S_g[(size_t)d * V + col] = S[i];
+            if (KIND == 0 && c == 0) n_g[d] = n[i];
+        }
+    }
+    if (KIND == 0 && threadIdx.x == 0) *m_g = m;
+}
+
+template <typename TA, int DPT>
+static int launch_memory_scan(const MemoryScanArgs& a, int R, cudaStream_t stream) {
+    const int CT = RC_THREADS / R;
+    const size_t smem = (size_t)(RC_CHUNK * (2 * a.D + CT + 5)) * sizeof(float);
+    if (smem > 48 * 1024) return GL_ERR_SMEM;
+    const dim3 grid((a.V + CT - 1) / CT, a.H, a.B);
+    if (a.kind == 0) return gl_launch(memory_scan_kernel<TA, DPT, 0>, grid, dim3(RC_THREADS), smem, stream, 1, a, R);
+    return gl_launch(memory_scan_kernel<TA, DPT, 1>, grid, dim3(RC_THREADS), smem, stream, 1, a, R);
+}
+
+static int memory_scan_lanes(int D) {               // lanes that share a column's rows
+    const int dpt = D <= 64 ? 8 : 32;
+    int R = 1;
+    while (R * dpt < D) R <<= 1;
+    return R;
+}
+
+// blocks of columns a head of these sizes is spread over; the state row's size follows from it
+GL_API int gl_memory_scan_tiles(int D, int V) {
+    if (D <= 0 || V <= 0 || D > 512) return GL_ERR_SHAPE;
+    const int CT = RC_THREADS / memory_scan_lanes(D);
+    return (V + CT - 1) / CT;
+}
+
+GL_API int gl_memory_scan(const MemoryScanArgs* args, int act_dtype, cudaStream_t stream) {
+    const MemoryScanArgs& a = *args;
+    if (a.B <= 0) return GL_OK;
+    if (a.H <= 0 || a.D <= 0 || a.V <= 0 || a.D > 512 || a.B > 65535 || a.H > 65535) return GL_ERR_SHAPE;
+    if (a.kind != 0 && a.kind != 1) return GL_ERR_SHAPE;
+    if (a.kind == 0 && !(a.cap > 0.f)) return GL_ERR_SHAPE;
+    const int dpt = a.D <= 64 ? 8 : 32;
+    const int R = memory_scan_lanes(a.D);
+    if (R > 32) return GL_ERR_SHAPE;
+    {
+        const int tiles = gl_memory_scan_tiles(a.D, a.V);
+        const long long need = (long long)a.H * a.D * a.V + (a.kind == 0 ? (long long)a.H * tiles * (a.D + 1) : 0);
+        if (a.state_stride < need) return GL_ERR_SHAPE;
+    }
+    if (act_dtype == GL_F32)
+        return dpt == 8 ? launch_memory_scan<float, 8>(a, R, stream) : launch_memory_scan<float, 32>(a, R, stream);
+    if (act_dtype == GL_BF16)
+        return dpt == 8 ? launch_memory_scan<__nv_bfloat16, 8>(a, R, stream)
+                        : launch_memory_scan<__nv_bfloat16, 32>(a, R, stream);
+    return GL_ERR_DTYPE;
+}
+
+// ---------------------------------------------------------------------------
+// Per-head unit norm of a memory's output, a weight and an optional gate:
+//   out[t, h, j] = o[t, h, j] / sqrt(mean_j o[t, h, :]^2 + eps) * w * sigmoid(gate[t, h*V + j])
+// w is [H*V] (w_per_head = 1) or [V] shared by the heads; gate (activation type, row pitch
+// gate_ld, first column gate_off) may be absent.  One warp per (token, head).
+// ---------------------------------------------------------------------------
+template <typename TA>
+__global__ void __launch_bounds__(128)
+head_norm_gate_kernel(const float* o, const float* __restrict__ w, const TA* gate, TA* __restrict__ out,
+                      long long items, int H, int V, int w_per_head, int gate_ld, int gate_off, float eps) {
+    gl_grid_launch_dependents();
+    gl_grid_wait();
+    const int lane = threadIdx.x & 31;
+    const long long item = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (item >= items) return;
+    const long long t = item / H;
+    const int h = (int)(item - t * H);
+    const float* src = o + (size_t)item * V;
+    float q = 0.f;
+    for (int j = lane; j < V; j += 32) { const float v = src[j]; q += v * v; }
+    const float inv = 1.0f / sqrtf(gl_warp_sum(q) / (float)V + eps);
+    for (int j = lane; j < V; j += 32) {
+        float y = src[j] * inv * w[w_per_head ? h * V + j : j];
+        if (gate) y *= rc_sigmoid(gl_load(gate + (size_t)t * gate_ld + gate_off + h * V + j));
+        gl_store(out + (size_t)item * V + j, y);
+    }
+}
+
+GL_API int gl_head_norm_gate(const float* o, const float* w, const void* gate, void* out, int T, int H, int V,
+                             int w_per_head, int gate_ld, int gate_off, float eps, int act_dtype, cudaStream_t stream) {
+    if (T <= 0) return GL_OK;
+    if (H <= 0 || V <= 0) return GL_ERR_SHAPE;
+    const long long items = (long long)T * H;
+    const dim3 grid((unsigned)((items + 3) / 4));
+    if (act_dtype == GL_F32)
+        return gl_launch(head_norm_gate_kernel<float>, grid, dim3(128), 0, stream, 1, o, w, (const float*)gate, (float*)out,
+                         items, H, V, w_per_head, gate_ld, gate_off, eps);
+    if (act_dtype == GL_BF16)
+        return gl_launch(head_norm_gate_kernel<__nv_bfloat16>, grid, dim3(128), 0, stream, 1, o, w, (const __nv_bfloat16*)gate,
+                         (__nv_bfloat16*)out, items, H, V, w_per_head, gate_ld, gate_off, eps);
+    return GL_ERR_DTYPE;
+}
+
+// ---------------------------------------------------------------------------
+// Short causal convolution per channel with bias and silu.  The filter's last tap is the current
+// token's; inputs before the run come from the sequence's state row (the last taps-1 inputs, oldest
+// first, zero at a sequence's start).  A second kernel then moves the run's last inputs into the row.
+// ---------------------------------------------------------------------------
+struct ConvArgs {
+    const void* x;            // [T, ld] activation type; the convolved channels start at column x_off
+    void* out;                // [T, C] activation type
+    const float* w;           // [C, taps]
+    const float* bias;        // [C]
+    float* state;             // [slots, state_stride]; the tail [C, taps-1] starts at tail_off
+    const int* tok_seq;       // [T]
+    const int* seq_slot;
+    const int* seq_qstart;
+    const int* seq_qlen;
+    int T, B, C, taps, ld, x_off, state_stride, tail_off;
+};
+
+template <typename TA>
+__global__ void __launch_bounds__(256)
+conv_silu_kernel(ConvArgs a) {
+    gl_grid_launch_dependents();
+    gl_grid_wait();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (long long)a.T * a.C) return;
+    const int t = (int)(i / a.C), c = (int)(i - (long long)t * a.C);
+    const int b = a.tok_seq[t];
+    const int idx = t - a.seq_qstart[b];
+    const int back = a.taps - 1;
+    const float* tail = a.state + (size_t)a.seq_slot[b] * a.state_stride + a.tail_off + (size_t)c * back;
+    float acc = a.bias[c];
+    for (int j = 0; j < a.taps; ++j) {
+        const int rel = idx - back + j;               // place in the run; negative: before it
+        const float v = rel >= 0 ? gl_load((const TA*)a.x + (size_t)(t - back + j) * a.ld + a.x_off + c) : tail[rel + back];
+        acc = fmaf(a.w[(size_t)c * a.taps + j], v, acc);
+    }
+    gl_store((TA*)a.out + (size_t)t * a.C + c, rc_silu(acc));
+}
+
+template <typename TA>
+__global__ void __launch_bounds__(256)
+conv_tail_kernel(ConvArgs a) {
+    gl_grid_launch_dependents();
+    gl_grid_wait();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (long long)a.B * a.C) return;
+    const int b = (int)(i / a.C), c = (int)(i - (long long)b * a.C);
+    const int back = a.taps - 1, qlen = a.seq_qlen[b], qstart = a.seq_qstart[b];
+    float* tail = a.state + (size_t)a.seq_slot[b] * a.state_stride + a.tail_off + (size_t)c * back;
+    for (int k = 0; k < back; ++k) {                  // ascending: a place is read before a lower one is written
+        const int rel = qlen - back + k;
+        tail[k] = rel >= 0 ? gl_load((const TA*)a.x + (size_t)(qstart + rel) * a.ld + a.x_off + c) : tail[qlen + k];
+    }
+}
+
+GL_API int gl_conv_silu(const ConvArgs* args, int act_dtype, cudaStream_t stream) {
+    const ConvArgs& a = *args;
+    if (a.T <= 0 || a.B <= 0) return GL_OK;
+    if (a.C <= 0 || a.taps <= 0) return GL_ERR_SHAPE;
+    const long long n = (long long)a.T * a.C, nb = (long long)a.B * a.C;
+    const dim3 g1((unsigned)((n + 255) / 256)), g2((unsigned)((nb + 255) / 256));
+    int rc;
+    if (act_dtype == GL_F32) {
+        rc = gl_launch(conv_silu_kernel<float>, g1, dim3(256), 0, stream, 1, a);
+        if (rc == 0 && a.taps > 1) rc = gl_launch(conv_tail_kernel<float>, g2, dim3(256), 0, stream, 1, a);
+        return rc;
+    }
+    if (act_dtype == GL_BF16) {
+        rc = gl_launch(conv_silu_kernel<__nv_bfloat16>, g1, dim3(256), 0, stream, 1, a);
+        if (rc == 0 && a.taps > 1) rc = gl_launch(conv_tail_kernel<__nv_bfloat16>, g2, dim3(256), 0, stream, 1, a);
+        return rc;
+    }
+    return GL_ERR_DTYPE;
+}
+
+// ---------------------------------------------------------------------------
+// Selective scan.  Per channel c and state n:
+//   dt = softplus(dtp[t, c]);  S[c, n] <- e^(dt A[c, n]) S[c, n] + dt x[t, c] B[t, n],  A = -e^(A_log)
+//   y[t, c] = (sum_n S[c, n] C[t, n] + D[c] x[t, c]) * silu(z[t, c])
+// A channel's states are spread over G adjacent lanes, up to 8 states a lane.
+// ---------------------------------------------------------------------------
+struct SelectiveScanArgs {
+    const void* x;            // [T, C] activation type (the convolution's output)
+    const float* dtp;         // [T, C] 32-bit: the step size before softplus, bias included
+    const void* bc;           // [T, 2N] activation type: B then C
+    const void* z;            // activation type, row pitch z_ld, first column z_off
+    void* out;                // [T, C] activation type
+    const float* a_log;       // [C, N]
+    const float* d_skip;      // [C]
+    float* state;             // [slots, state_stride], S [C, N] first
+    const int* seq_slot;
+    const int* seq_qstart;
+    const int* seq_qlen;
+    int B, C, N, z_ld, z_off, state_stride;
+};
+
+#define SS_NPT 8
+
+template <typename TA>
+__global__ void __launch_bounds__(RC_THREADS)
+selective_scan_kernel(SelectiveScanArgs a, int G) {
+    extern __shared__ float smem[];
+    gl_grid_launch_dependents();
+    gl_grid_wait();
+    const int N = a.N, C = a.C;
+    const int CPB = RC_THREADS / G;
+    const int b = blockIdx.y, c0 = blockIdx.x * CPB;
+    const int g = threadIdx.x % G, cl = threadIdx.x / G;
+    const int c = c0 + cl;
+    const bool live = c < C;
+    const int qlen = a.seq_qlen[b], qstart = a.seq_qstart[b];
+    float* Bs = smem;                                 // [CHUNK][N]
+    float* Cs = Bs + RC_CHUNK * N;                    // [CHUNK][N]
+    float* ds = Cs + RC_CHUNK * N;                    // [CHUNK][CPB] step sizes
+    float* xs = ds + RC_CHUNK * CPB;                  // [CHUNK][CPB]
+    float* zs = xs + RC_CHUNK * CPB;                  // [CHUNK][CPB]
+    float* S_g = a.state + (size_t)a.seq_slot[b] * a.state_stride + (size_t)(live ? c : 0) * N;
+    float S[SS_NPT], A[SS_NPT];
+#pragma unroll
+    for (int i = 0; i < SS_NPT; ++i) {
+        const int n = g + G * i;
+        const bool ok = live && n < N;
+        S[i] = ok ? S_g[n] : 0.f;
+        A[i] = ok ? -expf(a.a_log[(size_t)c * N + n]) : 0.f;
+    }
+    const float dskip = live ? a.d_skip[c] : 0.f;
+    for (int s0 = 0; s0 < qlen; s0 += RC_CHUNK) {
+        const int ns = min(RC_CHUNK, qlen - s0);
+        __syncthreads();
+        for (int e = threadIdx.x; e < ns * N; e += RC_THREADS) {
+            const int s = e / N, n = e - s * N;
+            const TA* row = (const TA*)a.bc + (size_t)(qstart + s0 + s) * 2 * N;
+            Bs[e] = gl_load(row + n);
+            Cs[e] = gl_load(row + N + n);
+        }
+        for (int e = threadIdx.x; e < ns * CPB; e += RC_THREADS) {
+            const int s = e / CPB, j = e - s * CPB;
+            const size_t t = (size_t)(qstart + s0 + s);
+            const bool ok = c0 + j < C;
+            ds[e] = ok ? rc_softplus(a.dtp[t * C + c0 + j]) : 0.f;
+            xs[e] = ok ? gl_load((const TA*)a.x + t * C + c0 + j) : 0.f;
+            zs[e] = ok ? gl_load((const TA*)a.z + t * a.z_ld + a.z_off + c0 + j) : 0.f;
+        }
+        __syncthreads();
+        for (int s = 0; s < ns; ++s) {
+            const float dt = ds[s * CPB + cl], x = xs[s * CPB + cl];
+            const float dx = dt * x;
+            const float* Bt = Bs + s * N;
+            const float* Ct = Cs + s * N;
+            float y = 0.f;
+#pragma unroll
+            for (int i = 0; i < SS_NPT; ++i) {
+                const int n = g + G * i;
+                if (n < N) {
+                    S[i] = fmaf(expf(dt * A[i]), S[i], dx * Bt[n]);
+                    y = fmaf(S[i], Ct[n], y);
+                }
+            }
+            for (int o = G >> 1; o > 0; o >>= 1) y += __shfl_xor_sync(0xffffffffu, y, o);
+            if (g == 0 && live) {
+                y = fmaf(dskip, x, y);
+                gl_store((TA*)a.out + (size_t)(qstart + s0 + s) * C + c, y * rc_silu(zs[s * CPB + cl]));
+            }
+        }
+    }
+    if (live) {
+#pragma unroll
+        for (int i = 0; i < SS_NPT; ++i) {
+            const int n = g + G * i;
+            if (n < N) S_g[n] = S[i];
+        }
+    }
+}
+
+GL_API int gl_selective_scan(const SelectiveScanArgs* args, int act_dtype, cudaStream_t stream) {
+    const SelectiveScanArgs& a = *args;
+    if (a.B <= 0) return GL_OK;
+    if (a.C <= 0 || a.N <= 0 || a.N > 32 * SS_NPT || a.B > 65535) return GL_ERR_SHAPE;
+    int G = 1;
+    while (G * SS_NPT < a.N) G <<= 1;
+    const int CPB = RC_THREADS / G;
+    const size_t smem = (size_t)RC_CHUNK * (2 * a.N + 3 * CPB) * sizeof(float);
+    const dim3 grid((a.C + CPB - 1) / CPB, a.B);
+    if (act_dtype == GL_F32) return gl_launch(selective_scan_kernel<float>, grid, dim3(RC_THREADS), smem, stream, 1, a, G);
+    if (act_dtype == GL_BF16)
+        return gl_launch(selective_scan_kernel<__nv_bfloat16>, grid, dim3(RC_THREADS), smem, stream, 1, a, G);
+    return GL_ERR_DTYPE;
+}

@@ -307,3 +307,93 @@ GL_API int gl_advance_decode(int* tokens, int* tok_pos, int* seq_ctx, const int*
     return gl_launch(advance_kernel, dim3(1), dim3(((B + 31) / 32) * 32), 0, stream, 1, tokens, tok_pos, seq_ctx, sampled,
                      history, counter, B, max_steps);
 }
+
+// ---------------------------------------------------------------------------
+// Gated feed-forward, between its products: out[t, j] = act(gu[t, j]) * gu[t, F + j], where a row
+// of gu holds the gate's F columns and then the up projection's.  32-bit arithmetic, one rounding.
+// ---------------------------------------------------------------------------
+template <typename TA>
+__global__ void __launch_bounds__(256)
+gated_act_kernel(const TA* gu, TA* __restrict__ out, long long n, int F, int act) {
+    gl_grid_launch_dependents();
+    gl_grid_wait();
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+        const long long t = i / F;
+        const int j = (int)(i - t * F);
+        const TA* row = gu + (size_t)t * 2 * F;
+        const float g = gl_load(row + j), u = gl_load(row + F + j);
+        gl_store(out + i, gl_activate<true>(g, act) * u);
+    }
+}
+
+GL_API int gl_gated_act(const void* gu, void* out, int T, int F, int act, int act_dtype, cudaStream_t stream) {
+    if (T <= 0) return GL_OK;
+    if (F <= 0) return GL_ERR_SHAPE;
+    const long long n = (long long)T * F;
+    const long long want = (n + 255) / 256;
+    const dim3 grid((unsigned)(want > 8192 ? 8192 : want));
+    if (act_dtype == GL_F32)
+        return gl_launch(gated_act_kernel<float>, grid, dim3(256), 0, stream, 1, (const float*)gu, (float*)out, n, F, act);
+    if (act_dtype == GL_BF16)
+        return gl_launch(gated_act_kernel<__nv_bfloat16>, grid, dim3(256), 0, stream, 1, (const __nv_bfloat16*)gu,
+                         (__nv_bfloat16*)out, n, F, act);
+    return GL_ERR_DTYPE;
+}
+
+// ---------------------------------------------------------------------------
+// Entering a pass of a looped range of layers: x[t, :] += base[t, :] + table[row, :]
+// (base, the stream as it left the embedding, may be absent; table: one learned vector per pass).
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+enter_pass_kernel(float* x, const float* base, const float* __restrict__ table, long long n, int D, int row) {
+    gl_grid_launch_dependents();
+    gl_grid_wait();
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+        float v = x[i];
+        if (base) v += base[i];
+        if (table) v += table[(size_t)row * D + (int)(i % D)];
+        x[i] = v;
+    }
+}
+
+GL_API int gl_enter_pass(float* x, const float* base, const float* table, int T, int D, int row, cudaStream_t stream) {
+    if (T <= 0) return GL_OK;
+    if (D <= 0 || row < 0) return GL_ERR_SHAPE;
+    const long long n = (long long)T * D;
+    const long long want = (n + 255) / 256;
+    return gl_launch(enter_pass_kernel, dim3((unsigned)(want > 8192 ? 8192 : want)), dim3(256), 0, stream, 1, x, base, table, n, D, row);
+}
+
+// ---------------------------------------------------------------------------
+// A branch's output normalised over the width and added: 
+//   out[t, :] = alpha * a[t, :] / sqrt(mean(a[t, :]^2) + eps) * w + add0[t, :] + add1[t, :] + add2[t, :]
+// (32-bit rows; the adds may be absent; out may be one of them).  One warp per row.
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(128)
+rms_scale_add_kernel(const float* a, const float* __restrict__ w, const float* add0, const float* add1, const float* add2,
+                     float* out, int R, int D, float eps, float alpha) {
+    gl_grid_launch_dependents();
+    gl_grid_wait();
+    const int lane = threadIdx.x & 31;
+    const int r = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (r >= R) return;
+    const float* src = a + (size_t)r * D;
+    float q = 0.f;
+    for (int d = lane; d < D; d += 32) { const float v = src[d]; q += v * v; }
+    const float inv = alpha / sqrtf(gl_warp_sum(q) / (float)D + eps);
+    for (int d = lane; d < D; d += 32) {
+        float y = src[d] * inv * w[d];
+        const size_t i = (size_t)r * D + d;
+        if (add0) y += add0[i];
+        if (add1) y += add1[i];
+        if (add2) y += add2[i];
+        out[i] = y;
+    }
+}
+
+GL_API int gl_rms_scale_add(const float* a, const float* w, const float* add0, const float* add1, const float* add2,
+                            float* out, int R, int D, float eps, float alpha, cudaStream_t stream) {
+    if (R <= 0) return GL_OK;
+    if (D <= 0) return GL_ERR_SHAPE;
+    return gl_launch(rms_scale_add_kernel, dim3((unsigned)((R + 3) / 4)), dim3(128), 0, stream, 1, a, w, add0, add1, add2, out, R, D, eps, alpha);
+}

@@ -43,6 +43,9 @@ class DecoderModel:
         self.spec = spec
         self.blocks = [build_block(b) for b in spec.layers]
         self.final_norm = build_norm(spec.final_norm)
+        self.embedding_norm = build_norm(spec.embedding_norm) if spec.embedding_norm is not None else None
+        self.pass_vectors: Optional[torch.Tensor] = None       # one learned vector per pass over a looped range
+        self._keeps_embedding = any(e.enter is not None and e.enter.add_embedding for e in spec.schedule)
         self.embedding: Optional[torch.Tensor] = None
         self.positions: Optional[torch.Tensor] = None          # learned absolute positions, if the spec has them
         self.head_weight: Optional[torch.Tensor] = None
@@ -60,6 +63,11 @@ class DecoderModel:
             p["positions"] = ParamSpec((s.position_table, s.hidden))
         for k, v in self.final_norm.parameters().items():
             p[f"final_norm/{k}"] = v
+        if self.embedding_norm is not None:
+            for k, v in self.embedding_norm.parameters().items():
+                p[f"embedding_norm/{k}"] = v
+        if s.pass_vectors:
+            p["pass_vectors"] = ParamSpec((s.pass_vectors, s.hidden), "vector", "bias")
         if not s.tie_embeddings:
             p["head/weight"] = ParamSpec((s.vocab, s.hidden))
         if s.head_bias:
@@ -75,6 +83,10 @@ class DecoderModel:
             b.load({k[len(pre):]: v for k, v in tensors.items() if k.startswith(pre)})
         self.final_norm.load({k[len("final_norm/"):]: v for k, v in tensors.items()
                               if k.startswith("final_norm/")})
+        if self.embedding_norm is not None:
+            self.embedding_norm.load({k[len("embedding_norm/"):]: v for k, v in tensors.items()
+                                      if k.startswith("embedding_norm/")})
+        self.pass_vectors = tensors["pass_vectors"] if self.spec.pass_vectors else None
         self.head_weight = self.embedding if self.spec.tie_embeddings else tensors["head/weight"]
         self.head_bias = tensors.get("head/bias")
         self._held = {}
@@ -82,7 +94,8 @@ class DecoderModel:
     @property
     def capturable(self) -> bool:
         """True if a step of this model can be recorded into a CUDA graph."""
-        return self.final_norm.capturable and all(b.capturable for b in self.blocks)
+        return (self.final_norm.capturable and all(b.capturable for b in self.blocks)
+                and (self.embedding_norm is None or self.embedding_norm.capturable))
 
     def weight_bytes(self) -> int:
         seen, n = set(), 0
@@ -97,7 +110,8 @@ class DecoderModel:
         yield self.positions
         yield self.head_weight
         yield self.head_bias
-        stack = list(self.blocks) + [self.final_norm]
+        yield self.pass_vectors
+        stack = list(self.blocks) + [self.final_norm] + ([self.embedding_norm] if self.embedding_norm is not None else [])
         while stack:
             part = stack.pop()
             for v in vars(part).values():
@@ -134,6 +148,13 @@ class DecoderModel:
         x = ops.embed(self.embedding, ctx.tokens, self.spec.embedding_scale)
         if self.positions is not None:
             ops.add_rows(self.positions, ctx.tok_pos, x)
+        if self.embedding_norm is not None:
+            x = self.embedding_norm.forward(x, torch.float32)
+        if self._keeps_embedding:
+            # later passes over a looped range add the stream as it is now; it is kept with the step's
+            # context (a captured step's context lives as long as its graphs)
+            ctx.scratch["embedding_output"] = x
+            x = x.clone()
         return x
 
     def run(self, x, ctx, cache, start: int, stop: int) -> None:
@@ -151,6 +172,9 @@ class DecoderModel:
         for e in self.spec.schedule[start:stop]:
             view = cache.view(e.cache, e.writes) if e.cache is not None else None
             block = self.blocks[e.layer]
+            if e.enter is not None:
+                ops.enter_pass(x, ctx.scratch["embedding_output"] if e.enter.add_embedding else None,
+                               self.pass_vectors, e.enter.index)
             if not repeat or not getattr(block, "launches_only", False):
                 block.forward(x, ctx, view)
                 continue
@@ -188,7 +212,11 @@ class DecoderModel:
         if view is None:
             return held
         ptrs = dict(held)
-        ptrs.update(_tensor_addresses(view, "cache/"))
+        if isinstance(view, (tuple, list)):            # a mixer made of several keeps several views
+            for j, v in enumerate(view):
+                ptrs.update(_tensor_addresses(v, f"cache[{j}]/"))
+        else:
+            ptrs.update(_tensor_addresses(view, "cache/"))
         return ptrs
 
     def finish(self, x, ctx) -> torch.Tensor:

@@ -24,6 +24,9 @@ from typing import Dict
 import numpy as np
 
 
+MAX_LIVE_REQUESTS = 128      # requests the replay keeps open at a time
+
+
 def run(model, lines, out_dir: str, emit=print) -> None:
     """Replay ``lines`` (an iterable of JSON strings) on a loaded Model."""
     os.makedirs(out_dir, exist_ok=True)
@@ -61,7 +64,7 @@ def main(argv=None) -> int:
     ap.add_argument("--dtype", required=True, choices=["bfloat16", "float32"])
     ap.add_argument("--out", required=True, help="folder that receives <step>.f32")
     ap.add_argument("--max-tokens", type=int, required=True,
-                    help="most tokens live requests hold at any time, each rounded up to 64")
+                    help="most tokens live requests hold at any time")
     ap.add_argument("--device", default="cuda:0")
     args = ap.parse_args(argv)
 
@@ -69,7 +72,10 @@ def main(argv=None) -> int:
         print(f"[trace_run] {msg}", file=sys.stderr, flush=True)
 
     from ..api import load
-    model = load(args.model, dtype=args.dtype, max_tokens=args.max_tokens, device=args.device, log=log)
+    # the cache counts whole pages of 64 positions: every live request may leave most of its last page unused
+    slots = max(1, min(int(args.max_tokens), MAX_LIVE_REQUESTS))
+    model = load(args.model, dtype=args.dtype, max_tokens=int(args.max_tokens) + 64 * slots, device=args.device,
+                 max_slots=slots, log=log)
 
     def emit(s):
         sys.stdout.write(s + "\n")

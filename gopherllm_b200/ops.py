@@ -915,6 +915,273 @@ def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] 
     return out if fork is None else (out, out_b)
 
 
+# ---------------------------------------------------------------------------
+# Mixers with per-sequence state (csrc/recurrent.cu), attention with mixed heads (csrc/attention_mixed.cu)
+class _MemoryScanArgs(Structure):
+    _fields_ = [("proj", c_void_p), ("out", c_void_p), ("state", c_void_p), ("lower", c_void_p),
+                ("seq_slot", c_void_p), ("seq_qstart", c_void_p), ("seq_qlen", c_void_p),
+                ("ld", c_int), ("q_off", c_int), ("k_off", c_int), ("v_off", c_int), ("i_off", c_int), ("f_off", c_int),
+                ("B", c_int), ("H", c_int), ("D", c_int), ("V", c_int), ("state_stride", c_int), ("kind", c_int),
+                ("cap", c_float), ("q_scale", c_float)]
+
+
+MEMORY_GATED, MEMORY_BOUNDED_FORGET = 0, 1
+_SCAN_THREADS = 128
+
+
+def memory_scan_tiles(D: int, V: int) -> int:
+    """Blocks of columns the scan spreads a head's [D, V] memory over (the rule of gl_memory_scan_tiles,
+    restated so that a state row can be sized without a compiled library)."""
+    if not 0 < D <= 512 or V <= 0:
+        raise KernelError(f"memory_scan takes 1..512 rows a head, got {D}")
+    dpt = 8 if D <= 64 else 32
+    lanes = 1
+    while lanes * dpt < D:
+        lanes *= 2
+    ct = _SCAN_THREADS // lanes
+    return -(-V // ct)
+
+
+def memory_state_size(kind: int, H: int, D: int, V: int) -> int:
+    """Floats of a sequence's state row: S [H, D, V]; the gated kind adds a normaliser [D] and a running
+    maximum for each block of columns of each head."""
+    n = H * D * V
+    if kind == MEMORY_GATED:
+        n += H * memory_scan_tiles(D, V) * (D + 1)
+    return n
+
+
+def memory_scan(kind: int, proj: torch.Tensor, state: torch.Tensor, ctx, H: int, D: int, V: int,
+                q_off: int, k_off: int, v_off: int, i_off: int, f_off: int,
+                lower: Optional[torch.Tensor] = None, cap: float = 0.0, q_scale: float = 1.0) -> torch.Tensor:
+    """A matrix memory's run over the step's tokens: float32 [T, H*V], each head's S^T q (divided by the
+    gated kind's normaliser); ``state`` [slots, size] float32 is read at ctx.seq_slot and written back.
+    ``proj`` [T, ld] holds the projections at the given column offsets."""
+    _need(proj, "proj")
+    _need(state, "state", torch.float32)
+    T, ld = proj.shape
+    if state.shape[1] < memory_state_size(kind, H, D, V):
+        raise KernelError("memory_scan: the state row is too small for these sizes")
+    if kind == MEMORY_BOUNDED_FORGET:
+        _need(lower, "lower", torch.float32, (H * D,))
+    out = empty((T, H * V), torch.float32, proj.device)
+    a = _MemoryScanArgs(proj.data_ptr(), out.data_ptr(), state.data_ptr(), _addr(lower),
+                        ctx.seq_slot.data_ptr(), ctx.seq_qstart.data_ptr(), ctx.seq_qlen.data_ptr(),
+                        ld, q_off, k_off, v_off, i_off, f_off, ctx.n_seqs, H, D, V, state.shape[1], kind, cap, q_scale)
+    fn = _lib("recurrent.cu").gl_memory_scan
+    _check(_launch(fn, byref(a), c_int(dtype_code(proj.dtype)), _stream()), "memory_scan")
+    return out
+
+
+def head_norm_gate(o: torch.Tensor, w: torch.Tensor, H: int, V: int, eps: float, out_dtype: torch.dtype,
+                   gate: Optional[torch.Tensor] = None, gate_off: int = 0) -> torch.Tensor:
+    """Each head of float32 ``o`` [T, H*V] divided by its root mean square, times ``w`` ([H*V], or [V]
+    shared by the heads), times sigmoid of the gate's columns gate_off.. of ``gate`` [T, ld] if given."""
+    _need(o, "o", torch.float32)
+    T = o.shape[0]
+    _need(o, "o", shape=(T, H * V))
+    _need(w, "w", torch.float32)
+    if w.numel() not in (V, H * V):
+        raise KernelError(f"head_norm_gate: weight of {w.numel()} elements fits neither {V} nor {H * V}")
+    if gate is not None:
+        _need(gate, "gate", out_dtype)
+    out = empty((T, H * V), out_dtype, o.device)
+    fn = _lib("recurrent.cu").gl_head_norm_gate
+    _check(_launch(fn, _ptr(o), _ptr(w), _ptr(gate), _ptr(out), c_int(T), c_int(H), c_int(V),
+                   c_int(0 if w.numel() == V else 1),
+                   c_int(0 if gate is None else gate.shape[1]), c_int(gate_off), c_float(eps),
+                   c_int(dtype_code(out_dtype)), _stream()), "head_norm_gate")
+    return out
+
+
+class _ConvArgs(Structure):
+    _fields_ = [("x", c_void_p), ("out", c_void_p), ("w", c_void_p), ("bias", c_void_p), ("state", c_void_p),
+                ("tok_seq", c_void_p), ("seq_slot", c_void_p), ("seq_qstart", c_void_p), ("seq_qlen", c_void_p),
+                ("T", c_int), ("B", c_int), ("C", c_int), ("taps", c_int), ("ld", c_int), ("x_off", c_int),
+                ("state_stride", c_int), ("tail_off", c_int)]
+
+
+def conv_silu(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor, state: torch.Tensor, tail_off: int, ctx,
+              x_off: int = 0) -> torch.Tensor:
+    """silu of a causal per-channel convolution over columns x_off.. of ``x`` [T, ld]; ``w`` [C, taps] with the
+    current token's tap last.  The inputs before a run come from ``state`` (the last taps-1 inputs of each
+    channel from column tail_off of the sequence's row on), which then takes the run's last inputs."""
+    _need(x, "x")
+    _need(w, "w", torch.float32)
+    C, taps = w.shape
+    _need(bias, "bias", torch.float32, (C,))
+    _need(state, "state", torch.float32)
+    T, ld = x.shape
+    if x_off + C > ld or tail_off + C * (taps - 1) > state.shape[1]:
+        raise KernelError("conv_silu: columns or state row too small")
+    out = empty((T, C), x.dtype, x.device)
+    a = _ConvArgs(x.data_ptr(), out.data_ptr(), w.data_ptr(), bias.data_ptr(), state.data_ptr(),
+                  ctx.tok_seq.data_ptr(), ctx.seq_slot.data_ptr(), ctx.seq_qstart.data_ptr(), ctx.seq_qlen.data_ptr(),
+                  T, ctx.n_seqs, C, taps, ld, x_off, state.shape[1], tail_off)
+    fn = _lib("recurrent.cu").gl_conv_silu
+    _check(_launch(fn, byref(a), c_int(dtype_code(x.dtype)), _stream()), "conv_silu", 2 if taps > 1 else 1)
+    return out
+
+
+class _SelectiveScanArgs(Structure):
+    _fields_ = [("x", c_void_p), ("dtp", c_void_p), ("bc", c_void_p), ("z", c_void_p), ("out", c_void_p),
+                ("a_log", c_void_p), ("d_skip", c_void_p), ("state", c_void_p),
+                ("seq_slot", c_void_p), ("seq_qstart", c_void_p), ("seq_qlen", c_void_p),
+                ("B", c_int), ("C", c_int), ("N", c_int), ("z_ld", c_int), ("z_off", c_int), ("state_stride", c_int)]
+
+
+SCAN_MAX_STATE = 256
+
+
+def selective_scan(x: torch.Tensor, dtp: torch.Tensor, bc: torch.Tensor, z: torch.Tensor, z_off: int,
+                   a_log: torch.Tensor, d_skip: torch.Tensor, state: torch.Tensor, ctx) -> torch.Tensor:
+    """The selective state-space scan of the step's tokens: x [T, C], dtp [T, C] float32 (step size before
+    softplus), bc [T, 2N] (input then output projection of the state), z the gate in columns z_off.. of its
+    tensor; state rows hold S [C, N] first.  Returns [T, C] in x's type."""
+    _need(x, "x")
+    T, C = x.shape
+    N = a_log.shape[1]
+    _need(dtp, "dtp", torch.float32, (T, C))
+    _need(bc, "bc", x.dtype, (T, 2 * N))
+    _need(z, "z", x.dtype)
+    _need(a_log, "a_log", torch.float32, (C, N))
+    _need(d_skip, "d_skip", torch.float32, (C,))
+    _need(state, "state", torch.float32)
+    if N > SCAN_MAX_STATE or state.shape[1] < C * N or z_off + C > z.shape[1]:
+        raise KernelError("selective_scan: sizes the kernel does not take")
+    out = empty((T, C), x.dtype, x.device)
+    a = _SelectiveScanArgs(x.data_ptr(), dtp.data_ptr(), bc.data_ptr(), z.data_ptr(), out.data_ptr(),
+                           a_log.data_ptr(), d_skip.data_ptr(), state.data_ptr(),
+                           ctx.seq_slot.data_ptr(), ctx.seq_qstart.data_ptr(), ctx.seq_qlen.data_ptr(),
+                           ctx.n_seqs, C, N, z.shape[1], z_off, state.shape[1])
+    fn = _lib("recurrent.cu").gl_selective_scan
+    _check(_launch(fn, byref(a), c_int(dtype_code(x.dtype)), _stream()), "selective_scan")
+    return out
+
+
+class _QkvRowNormArgs(Structure):
+    _fields_ = [("qkv", c_void_p), ("q_out", c_void_p), ("k_cache", c_void_p), ("v_cache", c_void_p),
+                ("cosv", c_void_p), ("sinv", c_void_p), ("q_gamma", c_void_p), ("k_gamma", c_void_p),
+                ("tok_seq", c_void_p), ("tok_pos", c_void_p), ("pages", c_void_p),
+                ("T", c_int), ("ld", c_int), ("nH", c_int), ("nKV", c_int), ("hd", c_int), ("vd", c_int),
+                ("half", c_int), ("max_pages", c_int), ("interleaved", c_int), ("write_kv", c_int),
+                ("eps", c_float), ("q_scale", c_float), ("n_pages", c_int)]
+
+
+def qkv_rownorm_to_cache(qkv: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, ctx, pages: torch.Tensor,
+                         num_heads: int, num_kv_heads: int, head_dim: int, value_dim: int, q_scale: float,
+                         cos: Optional[torch.Tensor], sin: Optional[torch.Tensor], interleaved: bool,
+                         q_gamma: Optional[torch.Tensor], k_gamma: Optional[torch.Tensor], eps: float,
+                         write_kv: bool = True) -> torch.Tensor:
+    """Queries and keys normalised over the whole projection (root mean square, weights [nH*hd] and
+    [nKV*hd]; None: no norm), rotated and scaled; keys and values written to the tokens' cache rows.
+    qkv [T, ld]: q, k, v side by side from column 0.  Returns q [T, nH*hd]."""
+    _need(qkv, "qkv")
+    T, ld = qkv.shape
+    nq, nk, nv = num_heads * head_dim, num_kv_heads * head_dim, num_kv_heads * value_dim
+    if ld < nq + nk + nv:
+        raise KernelError("qkv_rownorm_to_cache: the projection's rows are too short")
+    if tuple(k_cache.shape[1:]) != (num_kv_heads, PAGE, head_dim) or tuple(v_cache.shape[1:]) != (num_kv_heads, PAGE, value_dim):
+        raise KernelError(f"cache pages do not fit: keys {tuple(k_cache.shape)}, values {tuple(v_cache.shape)}")
+    half = 0
+    if cos is not None:
+        half = cos.shape[-1]
+        _need(cos, "cos", torch.float32, (T, half))
+        _need(sin, "sin", torch.float32, (T, half))
+    if q_gamma is not None:
+        _need(q_gamma, "q_gamma", torch.float32, (nq,))
+    if k_gamma is not None:
+        _need(k_gamma, "k_gamma", torch.float32, (nk,))
+    q = empty((T, nq), qkv.dtype, qkv.device)
+    a = _QkvRowNormArgs(qkv.data_ptr(), q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), _addr(cos), _addr(sin),
+                        _addr(q_gamma), _addr(k_gamma), ctx.tok_seq.data_ptr(), ctx.tok_pos.data_ptr(), pages.data_ptr(),
+                        T, ld, num_heads, num_kv_heads, head_dim, value_dim, half, pages.shape[-1],
+                        1 if interleaved else 0, 1 if write_kv else 0, eps, q_scale, k_cache.shape[0])
+    fn = _lib("qkv_cache.cu").gl_qkv_rownorm_cache
+    _check(_launch(fn, byref(a), c_int(dtype_code(qkv.dtype)), c_int(dtype_code(k_cache.dtype)), _stream()),
+           "qkv_rownorm_to_cache")
+    return q
+
+
+class _MixedAttnArgs(Structure):
+    _fields_ = [("q", c_void_p), ("pairs", c_void_p), ("out", c_void_p), ("k_cache", c_void_p), ("v_cache", c_void_p),
+                ("mix", c_void_p), ("seq_qstart", c_void_p), ("seq_qlen", c_void_p), ("seq_ctx", c_void_p), ("pages", c_void_p),
+                ("T", c_int), ("B", c_int), ("nH", c_int), ("nKV", c_int), ("hd", c_int), ("vd", c_int),
+                ("max_pages", c_int), ("window", c_int), ("max_qlen", c_int), ("n_pages", c_int)]
+
+
+def attention_mixed(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, ctx, pages: torch.Tensor,
+                    num_heads: int, num_kv_heads: int, head_dim: int, value_dim: int,
+                    mix: Optional[torch.Tensor] = None, window: int = 0) -> torch.Tensor:
+    """Causal softmax attention of scaled queries [T, nH*hd] over the paged cache; with ``mix`` [nH, nH]
+    head h applies sum_g mix[h, g] * (head g's softmax weights) to the values of its own key/value
+    head.  Returns [T, nH*vd] in q's type."""
+    _need(q, "q")
+    T = q.shape[0]
+    _need(q, "q", shape=(T, num_heads * head_dim))
+    if mix is not None:
+        _need(mix, "mix", torch.float32, (num_heads, num_heads))
+    n_val = num_kv_heads if mix is not None else 1
+    pairs = empty((T, num_heads, n_val, value_dim), torch.float32, q.device)
+    out = empty((T, num_heads * value_dim), q.dtype, q.device)
+    a = _MixedAttnArgs(q.data_ptr(), pairs.data_ptr(), out.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), _addr(mix),
+                       ctx.seq_qstart.data_ptr(), ctx.seq_qlen.data_ptr(), ctx.seq_ctx.data_ptr(), pages.data_ptr(),
+                       T, ctx.n_seqs, num_heads, num_kv_heads, head_dim, value_dim, pages.shape[-1], window,
+                       ctx.max_qlen, k_cache.shape[0])
+    fn = _lib("attention_mixed.cu").gl_attention_mixed
+    _check(_launch(fn, byref(a), c_int(dtype_code(q.dtype)), c_int(dtype_code(k_cache.dtype)), _stream()),
+           "attention_mixed", 2)
+    return out
+
+
+def gated_act(gu: torch.Tensor, act) -> torch.Tensor:
+    """act(gate) * up for rows that hold the gate's columns and then the up projection's."""
+    _need(gu, "gu")
+    T, F2 = gu.shape
+    if F2 % 2 or act not in ACTIVATIONS:
+        raise KernelError("gated_act: rows of gate and up columns and a known activation expected")
+    out = empty((T, F2 // 2), gu.dtype, gu.device)
+    fn = _lib("rowwise.cu").gl_gated_act
+    _check(_launch(fn, _ptr(gu), _ptr(out), c_int(T), c_int(F2 // 2), c_int(ACTIVATIONS[act]),
+                   c_int(dtype_code(gu.dtype)), _stream()), "gated_act")
+    return out
+
+
+def enter_pass(x: torch.Tensor, base: Optional[torch.Tensor], table: Optional[torch.Tensor], row: int) -> torch.Tensor:
+    """x += base + table[row] on the float32 residual stream (either may be None)."""
+    _need(x, "x", torch.float32)
+    T, D = x.shape
+    if base is not None:
+        _need(base, "base", torch.float32, (T, D))
+    if table is not None:
+        _need(table, "table", torch.float32)
+        if table.shape[1] != D or not 0 <= row < table.shape[0]:
+            raise KernelError(f"enter_pass: row {row} of a table {tuple(table.shape)} for width {D}")
+    fn = _lib("rowwise.cu").gl_enter_pass
+    _check(_launch(fn, _ptr(x), _ptr(base), _ptr(table), c_int(T), c_int(D), c_int(row), _stream()), "enter_pass")
+    return x
+
+
+def rms_scale_add(a: torch.Tensor, w: torch.Tensor, eps: float, alpha: float, adds=(), out: Optional[torch.Tensor] = None):
+    """out = alpha * a / sqrt(mean(a^2) + eps) * w + sum(adds), float32 rows; up to three adds."""
+    _need(a, "a", torch.float32)
+    R, D = a.shape
+    _need(w, "w", torch.float32, (D,))
+    adds = list(adds)
+    if len(adds) > 3:
+        raise KernelError("rms_scale_add adds at most three tensors")
+    for t in adds:
+        _need(t, "add", torch.float32, (R, D))
+    adds += [None] * (3 - len(adds))
+    if out is None:
+        out = empty((R, D), torch.float32, a.device)
+    _need(out, "out", torch.float32, (R, D))
+    fn = _lib("rowwise.cu").gl_rms_scale_add
+    _check(_launch(fn, _ptr(a), _ptr(w), _ptr(adds[0]), _ptr(adds[1]), _ptr(adds[2]), _ptr(out), c_int(R), c_int(D),
+                   c_float(eps), c_float(alpha), _stream()), "rms_scale_add")
+    return out
+
+
 def wait_failures(clear: bool = False) -> dict:
     """Which of the loaded libraries recorded a bounded wait that ran out (what they computed since is
     invalid): library name -> 1, 0, or -1 if the word could not be read.  ``clear`` sets the words back

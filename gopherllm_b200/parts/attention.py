@@ -132,4 +132,90 @@ class Attention(Mixer):
 
 
 
+class MixedHeadAttention(Mixer):
+    """Softmax attention whose heads talk to one another after the softmax, over the paged cache.
+
+    q, k, v projections without bias (one product; values of size ``value_dim`` per head); with option
+    ``qk_norm`` = "projection" the whole q row and the whole k row of a token are RMS-normed (weights of
+    the rows' sizes, option ``norm_eps``) before the heads are split; position encoding on q and k; score
+    = (q . k) * q_scale; causal softmax per head; with option ``talk`` a learned table M [heads, heads] mixes
+    the heads' weights, w_h = sum_g M[h, g] p_g, and head h applies w_h to the values of its own key/value
+    head; output projection.  The sum over keys is linear, so the kernel computes every pair (query head's
+    weights, value head) once and mixes the results (csrc/attention_mixed.cu)."""
+
+    deferred_add = True
+    capturable = True
+    launches_only = True
+
+    def __init__(self, spec: MixerSpec):
+        if spec.num_heads % spec.num_kv_heads:
+            raise ValueError("num_heads must be a multiple of num_kv_heads")
+        self.spec = spec
+        self.vdim = spec.value_dim or spec.head_dim
+        if spec.head_dim > 256 or self.vdim > 256:
+            raise ValueError(f"head sizes {spec.head_dim}/{self.vdim} exceed what the attention kernels take (256)")
+        scope = spec.option("qk_norm", None)
+        if scope not in (None, "projection"):
+            raise ValueError(f"qk_norm {scope!r}: this mixer norms over the whole projection or not at all")
+        self.row_norm = scope == "projection"
+        self.talk = bool(spec.option("talk", False))
+        self.eps = float(spec.option("norm_eps", 1e-6))
+        self.position = build_position(spec.position)
+        self.w_qkv = self.w_out = self.q_gamma = self.k_gamma = self.mix = None
+
+    def parameters(self) -> Dict[str, ParamSpec]:
+        s = self.spec
+        q, kv, vv = s.num_heads * s.head_dim, s.num_kv_heads * s.head_dim, s.num_kv_heads * self.vdim
+        p = {"q.weight": ParamSpec((q, s.hidden)), "k.weight": ParamSpec((kv, s.hidden)),
+             "v.weight": ParamSpec((vv, s.hidden)), "o.weight": ParamSpec((s.hidden, s.num_heads * self.vdim))}
+        if self.row_norm:
+            p["q_norm.weight"] = ParamSpec((q,), "vector", "gamma")
+            p["k_norm.weight"] = ParamSpec((kv,), "vector", "gamma")
+        if self.talk:
+            p["talk"] = ParamSpec((s.num_heads, s.num_heads), "vector", "wide")
+        return p
+
+    def load(self, t: Dict[str, torch.Tensor]) -> None:
+        ws = [t["q.weight"], t["k.weight"], t["v.weight"]]
+        if len({w.dtype for w in ws}) > 1:
+            ws = [w.float() for w in ws]
+        n = sum(w.shape[0] for w in ws)
+        if n % 8:                                       # output rows of whole 16-byte units
+            ws.append(torch.zeros((8 - n % 8, ws[0].shape[1]), dtype=ws[0].dtype, device=ws[0].device))
+        self.w_qkv = torch.cat(ws, dim=0).contiguous()
+        self.w_out = t["o.weight"]
+        self.q_gamma, self.k_gamma = t.get("q_norm.weight"), t.get("k_norm.weight")
+        self.mix = t.get("talk")
+
+    def cache_request(self):
+        s = self.spec
+        return KVRequest(s.num_kv_heads, s.head_dim, s.window, value_dim=0 if self.vdim == s.head_dim else self.vdim)
+
+    def products(self):
+        return [("qkv", self.w_qkv, None, None), ("o", self.w_out, None, None)]
+
+    def until_last(self, xn, ctx, cache, first=None):
+        s = self.spec
+        qkv = first if first is not None else ops.linear(xn, self.w_qkv, None, out_dtype=ctx.act_dtype)
+        tables = self.position.tables(ctx)
+        cos, sin = tables if tables is not None else (None, None)
+        pages = ctx.pages[cache.group]
+        q = ops.qkv_rownorm_to_cache(qkv, cache.k, cache.v, ctx, pages, s.num_heads, s.num_kv_heads, s.head_dim,
+                                     self.vdim, s.q_scale, cos, sin, s.position.interleaved,
+                                     self.q_gamma, self.k_gamma, self.eps, write_kv=cache.writes)
+        o = ops.attention_mixed(q, cache.k, cache.v, ctx, pages, s.num_heads, s.num_kv_heads, s.head_dim, self.vdim,
+                                mix=self.mix, window=s.window)
+        return o, self.w_out, None
+
+    def forward(self, xn, ctx, cache, add: Sequence[torch.Tensor], out=None) -> torch.Tensor:
+        if len(add) > 2:
+            raise ValueError("at most two tensors can be added in the projection's epilogue")
+        o, w, _ = self.until_last(xn, ctx, cache)
+        add = [a() if callable(a) else a for a in add]
+        a0 = add[0] if len(add) > 0 else None
+        a1 = add[1] if len(add) > 1 else None
+        return ops.linear(o, w, None, add0=a0, add1=a1, out_dtype=torch.float32, out=out)
+
+
 register_mixer("attention", Attention)
+register_mixer("attention_mixed", MixedHeadAttention)

@@ -20,10 +20,12 @@ class ParamSpec:
     """One tensor a part owns.
 
     kind: "matrix" (kept in the stored 16/32-bit type), "vector" (held in
-    float32: the reference reads every 1-D tensor as float32, model.go:2519-2528)
+    float32 whatever its shape: the reference reads every 1-D tensor as float32,
+    model.go:2519-2528; small tables that enter 32-bit arithmetic are held the same way)
     or "table_int" (held as int32).
     init: how the random-weights mode fills it: "normal" N(0, initializer_range),
-    "bias"/"beta" N(0, 0.02), "gamma" 1 + N(0, 0.02), "zeros".
+    "bias"/"beta" N(0, 0.02), "gamma" 1 + N(0, 0.02), "zeros", "unit" sigmoid(N(0, 1)) in (0, 1),
+    "wide" N(0, 1).
     optional: a missing tensor is replaced by zeros (model.go:2229-2231).
     """
     shape: Tuple[int, ...]
@@ -39,6 +41,7 @@ class KVRequest:
     num_kv_heads: int
     head_dim: int
     window: int = 0
+    value_dim: int = 0        # size of a head's values where it differs from head_dim (0: the same)
 
 
 @dataclass(frozen=True)

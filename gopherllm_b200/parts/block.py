@@ -22,14 +22,15 @@ class AssembledBlock(Block):
         self.norm = build_norm(spec.norm)
         self.norm2 = build_norm(spec.norm2) if spec.norm2 is not None else None
         self.mixer = build_mixer(spec.mixer)
-        self.ffn = build_feed_forward(spec.ffn)
+        self.ffn = build_feed_forward(spec.ffn) if spec.ffn is not None else None
 
     def children(self) -> Dict[str, object]:
         c = {"norm": self.norm}
         if self.norm2 is not None:
             c["norm2"] = self.norm2
         c["mixer"] = self.mixer
-        c["ffn"] = self.ffn
+        if self.ffn is not None:
+            c["ffn"] = self.ffn
         return c
 
     def parameters(self) -> Dict[str, ParamSpec]:
@@ -158,5 +159,33 @@ class SequentialBlock(AssembledBlock):
         return x
 
 
+class TwoNormParallelBlock(AssembledBlock):
+    """x <- x + (mixer(norm(x)) + ffn(norm2(x))): both branches read the same x, each through a norm of
+    its own.  A layer without a feed-forward (``spec.ffn`` None, no norm2) is x <- x + mixer(norm(x))."""
+
+    def __init__(self, spec: BlockSpec):
+        if (spec.ffn is None) != (spec.norm2 is None):
+            raise ValueError("the second norm comes with the feed-forward: both or neither")
+        super().__init__(spec)
+
+    def forward(self, x, ctx, cache):
+        xn = self.norm.forward(x, ctx.act_dtype)
+        if self.ffn is None:
+            self.mixer.forward(xn, ctx, cache, (x,), x)
+            return x
+        xn2 = self.norm2.forward(x, ctx.act_dtype)
+        if self.ffn.until_last is not None and self.mixer.until_last is not None:
+            # the branches' last products end on the same rows and columns: one product over the joined K
+            # where the kernels can, added onto the residual stream in its epilogue
+            h, w2, b2 = self.ffn.until_last(xn2, ctx)
+            o, wo, bo = self.mixer.until_last(xn, ctx, cache)
+            ops.linear_pair(h, w2, b2, o, wo, bo, add0=x, out=x)
+            return x
+        y = self.ffn.forward(xn2, ctx, (), None)
+        self.mixer.forward(xn, ctx, cache, (y, x), x)
+        return x
+
+
 register_block("parallel", ParallelBlock)
+register_block("parallel_two_norms", TwoNormParallelBlock)
 register_block("sequential", SequentialBlock)

@@ -59,4 +59,54 @@ class DenseFeedForward(FeedForward):
         return ops.linear(h, self.w_down, self.b_down, add0=a0, add1=a1, out=out)
 
 
+class GatedFeedForward(FeedForward):
+    """down(act(gate(x)) * up(x)), biases optional: the gate's and the up projection's rows are one
+    product, the activation and the multiplication one pass between the products (32-bit arithmetic,
+    one rounding), the additions to the residual in the last product's epilogue."""
+    capturable = True
+    launches_only = True
+
+    def __init__(self, spec: FeedForwardSpec):
+        if spec.activation not in ops.ACTIVATIONS:
+            raise ValueError(f"activation {spec.activation!r} unknown")
+        self.spec = spec
+        self.w_gu = self.b_gu = self.w_down = self.b_down = None
+
+    def parameters(self) -> Dict[str, ParamSpec]:
+        s = self.spec
+        p = {"gate.weight": ParamSpec((s.intermediate, s.hidden)), "up.weight": ParamSpec((s.intermediate, s.hidden)),
+             "down.weight": ParamSpec((s.hidden, s.intermediate))}
+        if s.bias:
+            p["gate.bias"] = ParamSpec((s.intermediate,), "vector", "bias")
+            p["up.bias"] = ParamSpec((s.intermediate,), "vector", "bias")
+            p["down.bias"] = ParamSpec((s.hidden,), "vector", "bias")
+        return p
+
+    def load(self, t: Dict[str, torch.Tensor]) -> None:
+        ws = [t["gate.weight"], t["up.weight"]]
+        if ws[0].dtype != ws[1].dtype:
+            ws = [w.float() for w in ws]
+        self.w_gu = torch.cat(ws, 0).contiguous()
+        self.w_down = t["down.weight"]
+        if self.spec.bias:
+            self.b_gu = torch.cat([t["gate.bias"], t["up.bias"]]).contiguous()
+            self.b_down = t["down.bias"]
+
+    def products(self):
+        return [("gate_up", self.w_gu, self.b_gu, None), ("down", self.w_down, self.b_down, None)]
+
+    def until_last(self, xn, ctx, first=None):
+        gu = first if first is not None else ops.linear(xn, self.w_gu, self.b_gu, out_dtype=ctx.act_dtype)
+        return ops.gated_act(gu, self.spec.activation), self.w_down, self.b_down
+
+    def forward(self, xn, ctx, add: Sequence[torch.Tensor], out=None) -> torch.Tensor:
+        if len(add) > 2:
+            raise ValueError("at most two tensors can be added in the projection's epilogue")
+        h, w, b = self.until_last(xn, ctx)
+        a0 = add[0] if len(add) > 0 else None
+        a1 = add[1] if len(add) > 1 else None
+        return ops.linear(h, w, b, add0=a0, add1=a1, out_dtype=torch.float32, out=out)
+
+
 register_feed_forward("dense", DenseFeedForward)
+register_feed_forward("gated", GatedFeedForward)

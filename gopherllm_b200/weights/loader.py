@@ -44,9 +44,12 @@ def tensor_table(model_parameters: Dict[str, ParamSpec], names) -> Dict[str, Tup
     ("sub/weight": a part inside the slot's part); ``names.layer`` gets it with dots for slashes,
     the way a part spells its own nested parameters ("q_norm.weight")."""
     table: Dict[str, Tuple[str, ParamSpec]] = {}
+    top = getattr(names, "top", None)      # a design whose files spell the model's own tensors its own way
     for key, spec in model_parameters.items():
         parts = key.split("/")
-        if parts[0] == "embedding" and len(parts) == 1:
+        if top is not None and parts[0] != "layers":
+            name = top(key)
+        elif parts[0] == "embedding" and len(parts) == 1:
             name = names.embedding
         elif parts[0] == "positions" and len(parts) == 1:
             name = getattr(names, "positions", None)
@@ -198,6 +201,10 @@ def random_tensor(name: str, spec: ParamSpec, seed: int, sigma: float, storage: 
         t = z.mul_(0.02).add_(1.0)
     elif spec.init == "zeros":
         t = z.zero_()
+    elif spec.init == "unit":                  # a bound or a share, strictly inside (0, 1)
+        t = torch.sigmoid(z)
+    elif spec.init == "wide":                  # N(0, 1): biases of gates that should not all sit at one half
+        t = z
     else:
         raise ValueError(f"{name}: unknown initialisation {spec.init!r}")
     return t.to(storage)
