@@ -4,6 +4,8 @@
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--context 2048] [--layers L]
     python bench.py --model phi-1.5          the same measurements at Phi-1.5's layer sizes
     python bench.py --ragged                 64 unequal prompts as one batch through Model.generate
+    python bench.py --design vopedra         prefill and decode of a Vopedra model at a few layer sizes beside a
+                                             Phi model of equal width, depth and feed-forward weights
 
 Prints one JSON line.  ``value`` is decoded tokens a second at the given batch and
 context, timed on the device over K decode steps that run back to back without the
@@ -115,6 +117,9 @@ def main():
     ap.add_argument("--sections", default="decode,e2e,prefill,points",
                     help="which measurements to run (for profiling a part): decode,e2e,prefill,points")
     ap.add_argument("--model", default="phi-2", choices=sorted(MODELS), help="whose layer sizes to run")
+    ap.add_argument("--design", default=None, choices=["vopedra"],
+                    help="instead: prefill and decode rates of another design at a few layer sizes, beside the Phi "
+                         "model of equal width and depth")
     ap.add_argument("--ragged", action="store_true",
                     help="instead: 64 prompts of 16..1536 tokens as one batch through Model.generate, 512 tokens "
                          "each at temperature 0.8, and a 32-bit check of 4 of them")
@@ -140,6 +145,8 @@ def main():
     from gopherllm_b200 import ops
     from gopherllm_b200.sampling.sampler import DeviceSampler, SamplerConfig, request_seed
 
+    if args.design == "vopedra":
+        return design_vopedra(args)
     pk, pk_src = peaks()
     label, sizes, weight_seed = MODELS[args.model]
     cfg = dict(sizes)
@@ -308,6 +315,95 @@ def main():
                           "frac_sustained": round(flops / (ms / 1e3) / (pk["bf16_tflops_sustained"] * 1e12), 4)
                           if pk.get("bf16_tflops_sustained") else None}
     print(json.dumps(out))
+    return 0
+
+
+def vopedra_sizes(width, heads, ff, runs_of_loop=2):
+    """A Vopedra model whose layers resemble a real model's at this width: six layers (matrix LSTM, selective
+    scan, attention beside a gated linear memory, twice), the middle four run twice: ten layer runs."""
+    hd = width // heads
+    mlstm = {"type": "mlstm", "mixer": {"heads": max(1, heads // 4), "dim": 2 * hd, "vdim": 4 * hd, "gate_cap": 15.0},
+             "mlp": {"kind": "dense", "ff": ff}}
+    mamba = {"type": "mamba1", "mixer": {"inner": 2 * width, "state": 16, "dt_rank": width // 16, "conv": 4},
+             "mlp": {"kind": "dense", "ff": ff}}
+    pair = {"type": "parallel", "mixer": {
+        "left": {"heads": heads, "kv_heads": max(1, heads // 4), "dim": hd, "vdim": hd, "rot": {"dims": hd // 2, "base": 10000.0},
+                 "scale": hd ** -0.5},
+        "right": {"heads": heads, "dim": hd // 2, "vdim": hd}}, "mlp": {"kind": "dense", "ff": ff}}
+    return {"architecture": "Vopedra", "vocab": 32000, "width": width, "norm": {"eps": 1e-6}, "initializer_range": 0.02,
+            "layers": [mlstm, mamba, pair, mlstm, mamba, pair], "loop": {"start": 1, "stop": 5, "times": runs_of_loop}}
+
+
+def design_vopedra(args):
+    """Prefill and decode rates of Vopedra models (random weights) beside Phi models of the same width, the
+    same number of layer runs and feed-forwards of the same number of weights.  One JSON line."""
+    import numpy as np
+    import torch
+    import gopherllm_b200 as gl
+    from gopherllm_b200.sampling.sampler import DeviceSampler, SamplerConfig, request_seed
+    pk, pk_src = peaks()
+    K = min(args.steps, 32)
+    rng = np.random.default_rng(4)
+
+    def measure(cfg, layers=None):
+        model = gl.load_random(cfg, seed=7, dtype="bfloat16", max_tokens=40 * 1024 + 4096, layers=layers)
+        eng, V = model.engine, model.spec.vocab
+        out = {"weight_bytes": eng.model.weight_bytes(), "layer_runs": len(model.spec.schedule)}
+        for T in (512, 2048):
+            toks = [int(t) for t in rng.integers(0, V, size=T)]
+            times = []
+            for i in range(4):
+                s = eng.open()
+                torch.cuda.synchronize()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                eng.step([(s, toks)])
+                e1.record()
+                torch.cuda.synchronize()
+                if i:
+                    times.append(e0.elapsed_time(e1))
+                eng.close(s)
+            out[f"prefill_{T}"] = {"ms": round(min(times), 3), "tokens_per_s": round(T / (min(times) / 1e3), 1)}
+        for batch in (1, 8, 32):
+            ctx = 1024
+            prompts = [[int(t) for t in rng.integers(0, V, size=ctx - K - 8)] for _ in range(batch)]
+            slots = [eng.open() for _ in range(batch)]
+            sampler = DeviceSampler(SamplerConfig.greedy(), [request_seed(5, i) for i in range(batch)], prompts, V, eng.device)
+            first = []
+            for i in range(0, batch, 8):
+                rows = list(range(i, min(batch, i + 8)))
+                logits = eng.step([(slots[j], prompts[j]) for j in rows])
+                first += sampler.sample(logits, torch.tensor(rows, dtype=torch.int32).to(eng.device)).tolist()
+            toks = eng.decode_loop(slots, first, 1, sampler)
+            toks = eng.decode_loop(slots, toks[-1].tolist(), 6, sampler)
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            eng.decode_loop(slots, toks[-1].tolist(), K, sampler)
+            e1.record()
+            torch.cuda.synchronize()
+            eng.check_device()
+            ms = e0.elapsed_time(e1) / K
+            for s in slots:
+                eng.close(s)
+            out[f"decode_b{batch}"] = {"ms_per_step": round(ms, 4), "tokens_per_s": round(batch / (ms / 1e3), 1),
+                                       "weights_frac_of_hbm": round(out["weight_bytes"] / (ms / 1e3) / 1e9 / pk["hbm_gbs"], 4)}
+        model.close()
+        del model, eng
+        torch.cuda.empty_cache()
+        return out
+
+    clocks = ClockSampler()
+    clocks.start()
+    rows = []
+    for width, heads, ff_gated, ff_plain in ((1024, 16, 2752, 4096), (2048, 32, 5504, 8192)):
+        v = measure(vopedra_sizes(width, heads, ff_gated))
+        phi = dict(PHI15, hidden_size=width, num_attention_heads=heads, num_key_value_heads=heads,
+                   intermediate_size=ff_plain, vocab_size=32000, num_hidden_layers=v["layer_runs"])
+        rows.append({"width": width, "heads": heads, "vopedra": v, "phi": measure(phi)})
+    print(json.dumps({"metric": "prefill and decode rates of Vopedra layer sizes beside Phi of equal width and depth (bf16)",
+                      "unit": "tokens/s", "n_gpus": 1, "dtype": "bf16", "data": "synthetic: random weights seed 7, uniform token ids",
+                      "decode_steps_timed": K, "decode_context": 1024, "peaks": pk_src, "clocks": clocks.stop(), "sizes": rows}))
     return 0
 
 

@@ -60,13 +60,13 @@ class MixerSpec:
     num_heads: int = 0
     num_kv_heads: int = 0
     head_dim: int = 0
-    value_dim: int = 0            # size of a head's values where it differs from head_dim (0: the same)
     window: int = 0
     q_scale: float = 1.0          # multiplies q after position encoding
     bias: bool = True
     qk_norm: Optional[NormSpec] = None
     position: PositionSpec = PositionSpec()
     extra: Tuple[Tuple[str, object], ...] = ()   # free-form options for other mixers
+    value_dim: int = 0            # size of a head's values where it differs from head_dim (0: the same)
 
     def option(self, key, default=None):
         return dict(self.extra).get(key, default)

@@ -127,7 +127,8 @@ def _talking_attention(cfg: VopedraConfig, m: dict, where: str) -> MixerSpec:
     dims = rot.get("dims", 0)
     if isinstance(dims, bool) or not isinstance(dims, int) or dims < 0 or dims % 2 or dims > dim:
         raise ValueError(f"config.json: {where}.rot.dims must be even and at most dim, is {dims!r}")
-    position = (PositionSpec("rope", dims, _positive(where + ".rot", rot, "base"), interleaved=False)
+    position = (PositionSpec("rope", dims, _positive(where + ".rot", rot, "base"), interleaved=False,
+                             extra=(("exact_angles", True),))
                 if dims > 0 else PositionSpec("none"))
     return MixerSpec(kind="attention_mixed", hidden=cfg.width, num_heads=heads, num_kv_heads=kv, head_dim=dim,
                      value_dim=_positive_int(where, m, "vdim"), q_scale=_positive(where, m, "scale"), bias=False,

@@ -266,6 +266,17 @@ static int launch_mixed(const MixedAttnArgs& a, cudaStream_t stream) {
     return gl_launch(head_mix_kernel<TA>, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, 1, a);
 }
 
+// the mixing kernel alone, behind a pairs kernel of another library
+GL_API int gl_head_mix(const MixedAttnArgs* args, int act_dtype, cudaStream_t stream) {
+    const MixedAttnArgs& a = *args;
+    if (a.T <= 0) return GL_OK;
+    const long long n = (long long)a.T * a.nH * a.vd;
+    const dim3 grid((unsigned)((n + 255) / 256));
+    if (act_dtype == GL_F32) return gl_launch(head_mix_kernel<float>, grid, dim3(256), 0, stream, 1, a) == 0 ? GL_OK : GL_ERR_LAUNCH;
+    if (act_dtype == GL_BF16) return gl_launch(head_mix_kernel<__nv_bfloat16>, grid, dim3(256), 0, stream, 1, a) == 0 ? GL_OK : GL_ERR_LAUNCH;
+    return GL_ERR_DTYPE;
+}
+
 template <typename TA, typename TC>
 static int dispatch_mixed(const MixedAttnArgs& a, cudaStream_t stream) {
     switch ((a.vd + 31) / 32) {

@@ -18,6 +18,13 @@ def head_dim_defines(head_dim: int) -> Tuple[str, ...]:
     return (f"GL_HEAD_DIM={int(head_dim)}",)
 
 
+def pair_dim_defines(head_dim: int, value_dim: int) -> Tuple[str, ...]:
+    """Definitions of a library compiled per (key size, value size)."""
+    if int(value_dim) == int(head_dim):
+        return (f"GL_HEAD_DIM={int(head_dim)}",)
+    return (f"GL_HEAD_DIM={int(head_dim)}", f"GL_VALUE_DIM={int(value_dim)}")
+
+
 def all_libraries(head_dims: Iterable[int] = ()) -> Iterator[Tuple[str, Tuple[str, ...]]]:
     for src in GENERAL:
         yield src, ()

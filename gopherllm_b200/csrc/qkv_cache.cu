@@ -30,6 +30,28 @@ GL_API int gl_rope_table(const int* pos, const float* inv_freq, float* cosv, flo
     return gl_launch(rope_table_kernel, dim3((n + 127) / 128), dim3(128), 0, stream, 1, pos, inv_freq, cosv, sinv, T, half);
 }
 
+// The same tables from 64-bit frequencies: the angle pos * freq is a 64-bit product, so a table entry is
+// the correctly rounded cosine of the exact angle whatever the position.
+__global__ void rope_table64_kernel(const int* pos, const double* __restrict__ freq,
+                                    float* __restrict__ cosv, float* __restrict__ sinv, int T, int half) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    gl_grid_launch_dependents();
+    gl_grid_wait();
+    if (i >= T * half) return;
+    const int t = i / half, p = i % half;
+    double s, c;
+    sincos((double)pos[t] * freq[p], &s, &c);
+    cosv[i] = (float)c;
+    sinv[i] = (float)s;
+}
+
+GL_API int gl_rope_table64(const int* pos, const double* freq, float* cosv, float* sinv,
+                           int T, int half, cudaStream_t stream) {
+    if (T <= 0 || half <= 0) return GL_OK;
+    const int n = T * half;
+    return gl_launch(rope_table64_kernel, dim3((n + 127) / 128), dim3(128), 0, stream, 1, pos, freq, cosv, sinv, T, half);
+}
+
 struct QkvCacheArgs {
     const void* qkv;          // [T, (nH + 2 nKV) * hd], activation type
     void* q_out;              // [T, nH * hd], activation type

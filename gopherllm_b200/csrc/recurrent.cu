@@ -22,6 +22,10 @@ __device__ __forceinline__ float rc_sigmoid(float x) { return 1.0f / (1.0f + exp
 __device__ __forceinline__ float rc_silu(float x) { return x / (1.0f + expf(-x)); }
 __device__ __forceinline__ float rc_log_sigmoid(float x) { return fminf(x, 0.0f) - log1pf(expf(-fabsf(x))); }
 __device__ __forceinline__ float rc_softplus(float x) { return x > 20.0f ? x : log1pf(expf(x)); }
+// e^x for a decay that is applied at every token: near one the factor comes from expm1f, which is
+// rounded once; expf's last-bit errors near one do not average out over a thousand tokens of a slowly
+// decaying state.
+__device__ __forceinline__ float rc_decay(float x) { return x > -0.5f ? 1.0f + expm1f(x) : expf(x); }
 
 // ---------------------------------------------------------------------------
 // Matrix memories.  Per head a state S [D, V]; a token's output is S^T q.
@@ -113,7 +117,7 @@ memory_scan_kernel(MemoryScanArgs a, int R) {
                 for (int s = 0; s < ns; ++s) {
                     const float gi = gs[s * 4 + 0], gf = gs[s * 4 + 1];
                     const float m_new = fmaxf(gf + m, gi);
-                    gs[s * 4 + 2] = expf(gf + m - m_new);
+                    gs[s * 4 + 2] = rc_decay(gf + m - m_new);
                     gs[s * 4 + 3] = expf(gi - m_new);
                     es[s] = expf(-m_new);
                     m = m_new;
@@ -415,7 +419,7 @@ selective_scan_kernel(SelectiveScanArgs a, int G) {
             for (int i = 0; i < SS_NPT; ++i) {
                 const int n = g + G * i;
                 if (n < N) {
-                    S[i] = fmaf(expf(dt * A[i]), S[i], dx * Bt[n]);
+                    S[i] = fmaf(rc_decay(dt * A[i]), S[i], dx * Bt[n]);
                     y = fmaf(S[i], Ct[n], y);
                 }
             }

@@ -323,12 +323,19 @@ def advance_decode(tokens, tok_pos, seq_ctx, sampled, history, counter) -> None:
 
 
 def rope_table(pos: torch.Tensor, inv_freq: torch.Tensor):
-    """cos and sin of float32(pos) * inv_freq, each [T, half] float32."""
+    """cos and sin of float32(pos) * inv_freq, each [T, half] float32.  With float64 frequencies the
+    angle is the 64-bit product pos * inv_freq."""
     _need(pos, "pos", torch.int32)
-    _need(inv_freq, "inv_freq", torch.float32)
     T, half = pos.numel(), inv_freq.numel()
     cosv = empty((T, half), torch.float32, pos.device)
     sinv = empty(cosv.shape, cosv.dtype, cosv.device)
+    if inv_freq.dtype == torch.float64:
+        _need(inv_freq, "inv_freq", torch.float64)
+        fn = _lib("qkv_cache.cu").gl_rope_table64
+        _check(_launch(fn, _ptr(pos), _ptr(inv_freq), _ptr(cosv), _ptr(sinv), c_int(T), c_int(half), _stream()),
+               "rope_table")
+        return cosv, sinv
+    _need(inv_freq, "inv_freq", torch.float32)
     fn = _lib("qkv_cache.cu").gl_rope_table
     _check(_launch(fn, _ptr(pos), _ptr(inv_freq), _ptr(cosv), _ptr(sinv), c_int(T), c_int(half), _stream()),
            "rope_table")
@@ -1110,12 +1117,24 @@ class _MixedAttnArgs(Structure):
                 ("max_pages", c_int), ("window", c_int), ("max_qlen", c_int), ("n_pages", c_int)]
 
 
+class _PairsArgs(Structure):
+    _fields_ = [("q", c_void_p), ("pairs", c_void_p), ("k_cache", c_void_p), ("v_cache", c_void_p),
+                ("seq_qstart", c_void_p), ("seq_qlen", c_void_p), ("seq_ctx", c_void_p), ("pages", c_void_p),
+                ("B", c_int), ("nH", c_int), ("nKV", c_int), ("nVal", c_int), ("max_pages", c_int), ("window", c_int),
+                ("max_qlen", c_int)]
+
+
+USE_PAIRS_TC = True
+
+
 def attention_mixed(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, ctx, pages: torch.Tensor,
                     num_heads: int, num_kv_heads: int, head_dim: int, value_dim: int,
                     mix: Optional[torch.Tensor] = None, window: int = 0) -> torch.Tensor:
     """Causal softmax attention of scaled queries [T, nH*hd] over the paged cache; with ``mix`` [nH, nH]
     head h applies sum_g mix[h, g] * (head g's softmax weights) to the values of its own key/value
-    head.  Returns [T, nH*vd] in q's type."""
+    head.  Returns [T, nH*vd] in q's type.  Prompts in bfloat16 with key and value sizes that are
+    multiples of 16 compute the (query head, value head) pairs on the tensor cores (a library per pair
+    of sizes); everything else runs the 32-bit kernels."""
     _need(q, "q")
     T = q.shape[0]
     _need(q, "q", shape=(T, num_heads * head_dim))
@@ -1128,8 +1147,17 @@ def attention_mixed(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
                        ctx.seq_qstart.data_ptr(), ctx.seq_qlen.data_ptr(), ctx.seq_ctx.data_ptr(), pages.data_ptr(),
                        T, ctx.n_seqs, num_heads, num_kv_heads, head_dim, value_dim, pages.shape[-1], window,
                        ctx.max_qlen, k_cache.shape[0])
-    fn = _lib("attention_mixed.cu").gl_attention_mixed
-    _check(_launch(fn, byref(a), c_int(dtype_code(q.dtype)), c_int(dtype_code(k_cache.dtype)), _stream()),
+    lib = _lib("attention_mixed.cu")
+    if (USE_PAIRS_TC and ctx.max_qlen > 1 and q.dtype == torch.bfloat16 and k_cache.dtype == torch.bfloat16
+            and head_dim % 16 == 0 and value_dim % 16 == 0 and not DEBUG_BOUNDS):
+        p = _PairsArgs(q.data_ptr(), pairs.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(),
+                       ctx.seq_qstart.data_ptr(), ctx.seq_qlen.data_ptr(), ctx.seq_ctx.data_ptr(), pages.data_ptr(),
+                       ctx.n_seqs, num_heads, num_kv_heads, n_val, pages.shape[-1], window, ctx.max_qlen)
+        fn = _lib("attention_mixed_tc.cu", catalog.pair_dim_defines(head_dim, value_dim)).gl_attention_pairs_tc
+        _check(_launch(fn, byref(p), _stream()), "attention_pairs_tc")
+        _check(_launch(lib.gl_head_mix, byref(a), c_int(dtype_code(q.dtype)), _stream()), "head_mix")
+        return out
+    _check(_launch(lib.gl_attention_mixed, byref(a), c_int(dtype_code(q.dtype)), c_int(dtype_code(k_cache.dtype)), _stream()),
            "attention_mixed", 2)
     return out
 

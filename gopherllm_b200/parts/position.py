@@ -35,12 +35,20 @@ class Rope(PositionEncoding):
         self._inv = None
 
     def tables(self, ctx):
-        key = ("rope", self.spec.rotary_dim, float(self.spec.theta))
+        exact = bool(self.spec.option("exact_angles", False))
+        key = ("rope", self.spec.rotary_dim, float(self.spec.theta), exact)
         hit = ctx.scratch.get(key)
         if hit is None:
             if self._inv is None or self._inv.device != ctx.device:
-                self._inv = torch.from_numpy(
-                    rope_inverse_frequencies(self.spec.rotary_dim, self.spec.theta)).to(ctx.device)
+                if exact:
+                    # frequencies theta^(-2i/d) and the angles pos * frequency in 64-bit: a table entry is then
+                    # the rounded cosine of the true angle at any position (a 32-bit angle is off by up to
+                    # position * 2^-24 radians, which a sharp head sees a thousand positions on)
+                    half = self.spec.rotary_dim // 2
+                    inv = np.float64(self.spec.theta) ** (-2.0 * np.arange(half, dtype=np.float64) / self.spec.rotary_dim)
+                else:
+                    inv = rope_inverse_frequencies(self.spec.rotary_dim, self.spec.theta)
+                self._inv = torch.from_numpy(inv).to(ctx.device)
             hit = ops.rope_table(ctx.tok_pos, self._inv)
             ctx.scratch[key] = hit
         return hit
