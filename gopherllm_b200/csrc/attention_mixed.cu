@@ -219,6 +219,156 @@ attn_pairs_decode_kernel(MixedAttnArgs a) {
     }
 }
 
+// One token a sequence, few heads a group: a block owns one key head of one sequence, that is the query
+// heads that share it, and every value head their weights are applied to.  A page of keys is read once
+// for all of the group's query heads (a thread a (head, key) score), the softmax of a head is kept by one
+// warp, and each warp accumulates one value head for all of the group's query heads, so a page of values
+// is read once per key head and not once per pair.
+#define AM_GTHREADS 256
+
+__device__ __forceinline__ float am_dot(const float* q, const __nv_bfloat16* k, int hd) {
+    float acc = 0.f;
+    if ((hd & 7) == 0) {
+        for (int d = 0; d < hd; d += 8) {
+            const uint4 raw = *(const uint4*)(k + d);
+            const __nv_bfloat162* p2 = (const __nv_bfloat162*)&raw;
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float2 f = __bfloat1622float2(p2[e]);
+                acc = fmaf(q[d + 2 * e], f.x, acc);
+                acc = fmaf(q[d + 2 * e + 1], f.y, acc);
+            }
+        }
+    } else {
+        for (int d = 0; d < hd; ++d) acc = fmaf(q[d], __bfloat162float(k[d]), acc);
+    }
+    return acc;
+}
+__device__ __forceinline__ float am_dot(const float* q, const float* k, int hd) {
+    float acc = 0.f;
+    for (int d = 0; d < hd; ++d) acc = fmaf(q[d], k[d], acc);
+    return acc;
+}
+
+template <typename TA, typename TC, int NACC, int GQ>
+__global__ void __launch_bounds__(AM_GTHREADS)
+attn_group_decode_kernel(MixedAttnArgs a) {
+    extern __shared__ float smem[];
+    gl_grid_launch_dependents();
+    gl_grid_wait();
+    const int hd = a.hd, vd = a.vd;
+    const int gq = a.nH / a.nKV;                        // query heads of the group (<= GQ)
+    float* qv = smem;                                   // [gq][hd]
+    float* sc = qv + gq * hd;                           // [gq][GL_PAGE] scores, then weights
+    float* corr = sc + gq * GL_PAGE;                    // [gq] rescaling of this page, then 1 / sum
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int b = blockIdx.y, kh = blockIdx.x;
+    const int nVal = a.mix ? a.nKV : 1;
+    const int p = a.seq_ctx[b];
+    const int lo = (a.window > 0 && p - a.window + 1 > 0) ? p - a.window + 1 : 0;
+    const int row = a.seq_qstart[b];
+    const TA* qsrc = (const TA*)a.q + ((size_t)row * a.nH + (size_t)kh * gq) * hd;
+    for (int i = threadIdx.x; i < gq * hd; i += AM_GTHREADS) qv[i] = gl_load(qsrc + i);
+    const int vh = a.mix ? warp : kh;                   // this warp's value head
+    const bool has_values = a.mix ? warp < a.nKV : warp == 0;
+    float acc[GQ][NACC];
+#pragma unroll
+    for (int g = 0; g < GQ; ++g)
+#pragma unroll
+        for (int i = 0; i < NACC; ++i) acc[g][i] = 0.f;
+    float m = -INFINITY, l = 0.f;                       // warp g < gq keeps head g's running maximum and sum
+    const int* pg = a.pages + (size_t)b * a.max_pages;
+    for (int page_i = lo / GL_PAGE; page_i <= p / GL_PAGE; ++page_i) {
+        const int page = gl_checked(pg[gl_checked(page_i, a.max_pages, GL_BAD_POSITION)], a.n_pages > 0 ? a.n_pages : 0x7fffffff, GL_BAD_PAGE);
+        const TC* kp = (const TC*)a.k_cache + ((size_t)page * a.nKV + kh) * GL_PAGE * hd;
+        const int j0 = page_i * GL_PAGE;
+        __syncthreads();                                // the page before is used up (and q is in place)
+        for (int item = threadIdx.x; item < gq * GL_PAGE; item += AM_GTHREADS) {
+            const int g = item / GL_PAGE, key = item - g * GL_PAGE;
+            const int j = j0 + key;
+            sc[item] = (j >= lo && j <= p) ? am_dot(qv + g * hd, kp + (size_t)key * hd, hd) : -INFINITY;
+        }
+        __syncthreads();
+        if (warp < gq) {
+            const float s0 = sc[warp * GL_PAGE + lane], s1 = sc[warp * GL_PAGE + 32 + lane];
+            const float m_new = fmaxf(m, gl_warp_max(fmaxf(s0, s1)));      // the page holds position lo or later: finite
+            const float p0 = s0 > -INFINITY ? expf(s0 - m_new) : 0.f, p1 = s1 > -INFINITY ? expf(s1 - m_new) : 0.f;
+            const float c = expf(m - m_new);                                 // m = -inf gives 0
+            l = l * c + gl_warp_sum(p0 + p1);
+            m = m_new;
+            sc[warp * GL_PAGE + lane] = p0;
+            sc[warp * GL_PAGE + 32 + lane] = p1;
+            if (lane == 0) corr[warp] = c;
+        }
+        __syncthreads();
+        if (has_values) {
+            const TC* vp = (const TC*)a.v_cache + ((size_t)page * a.nKV + vh) * GL_PAGE * vd;
+#pragma unroll
+            for (int g = 0; g < GQ; ++g) {
+                if (g < gq) {
+                    const float c = corr[g];
+#pragma unroll
+                    for (int i = 0; i < NACC; ++i) acc[g][i] *= c;
+                }
+            }
+            const int kmin = max(0, lo - j0), kmax = min(GL_PAGE, p - j0 + 1);   // written keys inside the window
+            // eight keys' values are asked for before the first is used: one after the other, every key
+            // would cost a trip to memory
+            for (int k0 = 0; k0 < GL_PAGE; k0 += 8) {
+                if (k0 + 8 <= kmin || k0 >= kmax) continue;
+                float v[8][NACC];
+#pragma unroll
+                for (int kk = 0; kk < 8; ++kk) {
+                    const bool ok = k0 + kk >= kmin && k0 + kk < kmax;
+#pragma unroll
+                    for (int i = 0; i < NACC; ++i) {
+                        const int d = lane + 32 * i;
+                        v[kk][i] = (ok && d < vd) ? gl_load(vp + (size_t)(k0 + kk) * vd + d) : 0.f;
+                    }
+                }
+#pragma unroll
+                for (int kk = 0; kk < 8; ++kk) {
+#pragma unroll
+                    for (int g = 0; g < GQ; ++g) {
+                        if (g < gq) {
+                            const float pk = sc[g * GL_PAGE + k0 + kk];
+#pragma unroll
+                            for (int i = 0; i < NACC; ++i) acc[g][i] = fmaf(pk, v[kk][i], acc[g][i]);
+                        }
+                    }
+                }
+            }
+        }
+    }
+    __syncthreads();
+    if (warp < gq && lane == 0) corr[warp] = l > 0.f ? 1.0f / l : 0.f;
+    __syncthreads();
+    if (has_values) {
+#pragma unroll
+        for (int g = 0; g < GQ; ++g) {
+            if (g < gq) {
+                float* o = a.pairs + (((size_t)row * a.nH + (size_t)kh * gq + g) * nVal + (a.mix ? vh : 0)) * vd;
+#pragma unroll
+                for (int i = 0; i < NACC; ++i) {
+                    const int d = lane + 32 * i;
+                    if (d < vd) o[d] = acc[g][i] * corr[g];
+                }
+            }
+        }
+    }
+}
+
+template <typename TA, typename TC, int NACC>
+static int launch_group_decode(const MixedAttnArgs& a, cudaStream_t stream) {
+    const int gq = a.nH / a.nKV;
+    const size_t smem = ((size_t)gq * a.hd + (size_t)gq * GL_PAGE + gq) * sizeof(float);
+    const dim3 grid(a.nKV, a.B);
+    if (gq <= 1) return gl_launch(attn_group_decode_kernel<TA, TC, NACC, 1>, grid, dim3(AM_GTHREADS), smem, stream, 1, a);
+    if (gq <= 2) return gl_launch(attn_group_decode_kernel<TA, TC, NACC, 2>, grid, dim3(AM_GTHREADS), smem, stream, 1, a);
+    if (gq <= 4) return gl_launch(attn_group_decode_kernel<TA, TC, NACC, 4>, grid, dim3(AM_GTHREADS), smem, stream, 1, a);
+    return gl_launch(attn_group_decode_kernel<TA, TC, NACC, 8>, grid, dim3(AM_GTHREADS), smem, stream, 1, a);
+}
+
 // out[t, h, :] = sum_g M[h, g] pairs[t, g, c(h), :]   (without a table: pairs[t, h, 0, :])
 template <typename TA>
 __global__ void __launch_bounds__(256)
@@ -247,7 +397,9 @@ template <typename TA, typename TC, int NACC>
 static int launch_mixed(const MixedAttnArgs& a, cudaStream_t stream) {
     const int pairs = a.nH * (a.mix ? a.nKV : 1);
     int rc;
-    if (a.max_qlen == 1) {
+    if (a.max_qlen == 1 && a.nH / a.nKV <= 8 && a.nKV <= AM_GTHREADS / 32 && NACC <= 4) {
+        rc = launch_group_decode<TA, TC, NACC>(a, stream);
+    } else if (a.max_qlen == 1) {
         const size_t smem = ((size_t)a.hd + (size_t)AM_DWARPS * (a.vd + 2)) * sizeof(float);
         rc = gl_launch(attn_pairs_decode_kernel<TA, TC, NACC>, dim3(pairs, a.B), dim3(AM_DWARPS * 32), smem, stream, 1, a);
     } else {

@@ -16,7 +16,8 @@
 #include "common.cuh"
 
 #define RC_THREADS 128
-#define RC_CHUNK 8          // tokens staged at a time
+#define MS_THREADS 256     // the matrix memories' blocks
+#define SS_CHUNK 16         // tokens the selective scan stages at a time
 
 __device__ __forceinline__ float rc_sigmoid(float x) { return 1.0f / (1.0f + expf(-x)); }
 __device__ __forceinline__ float rc_silu(float x) { return x / (1.0f + expf(-x)); }
@@ -25,7 +26,10 @@ __device__ __forceinline__ float rc_softplus(float x) { return x > 20.0f ? x : l
 // e^x for a decay that is applied at every token: near one the factor comes from expm1f, which is
 // rounded once; expf's last-bit errors near one do not average out over a thousand tokens of a slowly
 // decaying state.
-__device__ __forceinline__ float rc_decay(float x) { return x > -0.5f ? 1.0f + expm1f(x) : expf(x); }
+__device__ __forceinline__ float rc_decay(float x) {
+    if (x > -0.5f) return 1.0f + expm1f(x);
+    return expf(x);
+}
 
 // ---------------------------------------------------------------------------
 // Matrix memories.  Per head a state S [D, V]; a token's output is S^T q.
@@ -34,8 +38,9 @@ __device__ __forceinline__ float rc_decay(float x) { return x > -0.5f ? 1.0f + e
 //       o = S'^T q / (max(|n'.q|, e^(-m')) + 1e-6).     m starts at 0 (a zeroed state row).
 //   kind 1, forget gate with a lower bound: f = l + (1-l) sigmoid(fpre) per row;
 //       S' = diag(f) S + (1-f) v^T;  o = S'^T q,  q = silu(qpre).
-// State row: S [H, D, V], then for kind 0 n [H, tiles, D] and m [H, tiles], tiles = the blocks of columns a
-// head is spread over (gl_memory_scan_tiles).
+// State row: S [H, D, V], then for kind 0 n [H, D] and m [H].  Every block of a head's columns reads n and m
+// when it starts, and blocks of one head may run one after the other, so the new n and m go to a scratch
+// [B, H, D + 1] first and a second kernel moves them into the rows once all blocks are done.
 // ---------------------------------------------------------------------------
 struct MemoryScanArgs {
     const void* proj;         // [T, ld] activation type: the joined projections of the step's tokens
@@ -48,34 +53,32 @@ struct MemoryScanArgs {
     int ld, q_off, k_off, v_off, i_off, f_off;
     int B, H, D, V, state_stride, kind;
     float cap, q_scale;
+    float* nm_next;           // kind 0: [B, H, D + 1] scratch for the new normaliser and maximum
 };
 
 template <typename TA, int DPT, int KIND>
-__global__ void __launch_bounds__(RC_THREADS)
-memory_scan_kernel(MemoryScanArgs a, int R) {
+__global__ void __launch_bounds__(MS_THREADS)
+memory_scan_kernel(MemoryScanArgs a, int R, int CH) {
     extern __shared__ float smem[];
     gl_grid_launch_dependents();
     gl_grid_wait();
     const int D = a.D, V = a.V, H = a.H;
-    const int CT = RC_THREADS / R;                    // columns of a block
+    const int CT = MS_THREADS / R;                    // columns of a block
     const int b = blockIdx.z, h = blockIdx.y, col0 = blockIdx.x * CT;
     const int r = threadIdx.x % R, c = threadIdx.x / R;
     const int col = col0 + c;
     const bool live = col < V;
     const int qlen = a.seq_qlen[b], qstart = a.seq_qstart[b];
     float* qs = smem;                                 // [CHUNK][D]
-    float* ks = qs + RC_CHUNK * D;                    // [CHUNK][D]   kind 0: k;  kind 1: f
-    float* vs = ks + RC_CHUNK * D;                    // [CHUNK][CT]
-    float* gs = vs + RC_CHUNK * CT;                   // [CHUNK][4]   kind 0: gi, gf, then keep, take; [.][3] reused
-    float* es = gs + RC_CHUNK * 4;                    // [CHUNK]      kind 0: e^(-m')
+    float* ks = qs + CH * D;                    // [CHUNK][D]   kind 0: k;  kind 1: f
+    float* vs = ks + CH * D;                    // [CHUNK][CT]
+    float* gs = vs + CH * CT;                   // [CHUNK][4]   kind 0: gi, gf, then keep, take; [.][3] reused
+    float* es = gs + CH * 4;                    // [CHUNK]      kind 0: e^(-m')
 
     float* srow = a.state + (size_t)a.seq_slot[b] * a.state_stride;
     float* S_g = srow + (size_t)h * D * V;
-    // every block of columns keeps its own copy of the head's normaliser and maximum: a block may start
-    // after another of the same head has finished and written its state back
-    const int tiles = gridDim.x;
-    float* n_g = srow + (size_t)H * D * V + ((size_t)h * tiles + blockIdx.x) * D;
-    float* m_g = srow + (size_t)H * D * V + (size_t)H * tiles * D + (size_t)h * tiles + blockIdx.x;
+    const float* n_g = srow + (size_t)H * D * V + (size_t)h * D;
+    const float* m_g = srow + (size_t)H * D * V + (size_t)H * D + h;
     float S[DPT], n[DPT];
 #pragma unroll
     for (int i = 0; i < DPT; ++i) {
@@ -85,10 +88,11 @@ memory_scan_kernel(MemoryScanArgs a, int R) {
     }
     float m = KIND == 0 ? *m_g : 0.f;                 // only thread 0 keeps it current
 
-    for (int s0 = 0; s0 < qlen; s0 += RC_CHUNK) {
-        const int ns = min(RC_CHUNK, qlen - s0);
+    for (int s0 = 0; s0 < qlen; s0 += CH) {
+        const int ns = min(CH, qlen - s0);
         __syncthreads();
-        for (int e = threadIdx.x; e < ns * D; e += RC_THREADS) {
+#pragma unroll 4
+        for (int e = threadIdx.x; e < ns * D; e += MS_THREADS) {
             const int s = e / D, d = e - s * D;
             const TA* row = (const TA*)a.proj + (size_t)(qstart + s0 + s) * a.ld;
             const float qp = gl_load(row + a.q_off + h * D + d);
@@ -101,7 +105,7 @@ memory_scan_kernel(MemoryScanArgs a, int R) {
                 ks[e] = l + (1.0f - l) * rc_sigmoid(gl_load(row + a.f_off + h * D + d));
             }
         }
-        for (int e = threadIdx.x; e < ns * CT; e += RC_THREADS) {
+        for (int e = threadIdx.x; e < ns * CT; e += MS_THREADS) {
             const int s = e / CT, j = e - s * CT;
             const TA* row = (const TA*)a.proj + (size_t)(qstart + s0 + s) * a.ld;
             vs[e] = col0 + j < V ? gl_load(row + a.v_off + h * V + col0 + j) : 0.f;
@@ -113,15 +117,23 @@ memory_scan_kernel(MemoryScanArgs a, int R) {
                 gs[threadIdx.x * 4 + 1] = rc_log_sigmoid(a.cap * tanhf(gl_load(row + a.f_off + h) / a.cap));
             }
             __syncthreads();
+            // the maximum is the only thing that goes from token to token here: one thread walks it, and the
+            // tokens' factors are then taken side by side
             if (threadIdx.x == 0) {
                 for (int s = 0; s < ns; ++s) {
-                    const float gi = gs[s * 4 + 0], gf = gs[s * 4 + 1];
-                    const float m_new = fmaxf(gf + m, gi);
-                    gs[s * 4 + 2] = rc_decay(gf + m - m_new);
-                    gs[s * 4 + 3] = expf(gi - m_new);
-                    es[s] = expf(-m_new);
+                    const float m_new = fmaxf(gs[s * 4 + 1] + m, gs[s * 4 + 0]);
+                    gs[s * 4 + 2] = m;
+                    gs[s * 4 + 3] = m_new;
                     m = m_new;
                 }
+            }
+            __syncthreads();
+            if (threadIdx.x < ns) {
+                const int s = threadIdx.x;
+                const float gi = gs[s * 4 + 0], gf = gs[s * 4 + 1], m_old = gs[s * 4 + 2], m_new = gs[s * 4 + 3];
+                gs[s * 4 + 2] = rc_decay(gf + m_old - m_new);
+                gs[s * 4 + 3] = expf(gi - m_new);
+                es[s] = expf(-m_new);
             }
         }
         __syncthreads();
@@ -170,34 +182,70 @@ memory_scan_kernel(MemoryScanArgs a, int R) {
         const int d = r + R * i;
         if (d < D) {
             if (live) S_g[(size_t)d * V + col] = S[i];
-            if (KIND == 0 && c == 0) n_g[d] = n[i];
+            if (KIND == 0 && blockIdx.x == 0 && c == 0) a.nm_next[((size_t)b * H + h) * (D + 1) + d] = n[i];
         }
     }
-    if (KIND == 0 && threadIdx.x == 0) *m_g = m;
+    if (KIND == 0 && blockIdx.x == 0 && threadIdx.x == 0) a.nm_next[((size_t)b * H + h) * (D + 1) + D] = m;
+}
+
+__global__ void __launch_bounds__(128)
+memory_commit_kernel(MemoryScanArgs a) {
+    gl_grid_launch_dependents();
+    gl_grid_wait();
+    const int b = blockIdx.y, h = blockIdx.x, H = a.H, D = a.D;
+    float* srow = a.state + (size_t)a.seq_slot[b] * a.state_stride + (size_t)H * D * a.V;
+    const float* src = a.nm_next + ((size_t)b * H + h) * (D + 1);
+    for (int d = threadIdx.x; d < D; d += blockDim.x) srow[(size_t)h * D + d] = src[d];
+    if (threadIdx.x == 0) srow[(size_t)H * D + h] = src[D];
 }
 
 template <typename TA, int DPT>
-static int launch_memory_scan(const MemoryScanArgs& a, int R, cudaStream_t stream) {
-    const int CT = RC_THREADS / R;
-    const size_t smem = (size_t)(RC_CHUNK * (2 * a.D + CT + 5)) * sizeof(float);
-    if (smem > 48 * 1024) return GL_ERR_SMEM;
-    const dim3 grid((a.V + CT - 1) / CT, a.H, a.B);
-    if (a.kind == 0) return gl_launch(memory_scan_kernel<TA, DPT, 0>, grid, dim3(RC_THREADS), smem, stream, 1, a, R);
-    return gl_launch(memory_scan_kernel<TA, DPT, 1>, grid, dim3(RC_THREADS), smem, stream, 1, a, R);
-}
-
-static int memory_scan_lanes(int D) {               // lanes that share a column's rows
-    const int dpt = D <= 64 ? 8 : 32;
+static int launch_memory_scan(const MemoryScanArgs& a, cudaStream_t stream) {
     int R = 1;
-    while (R * dpt < D) R <<= 1;
-    return R;
+    while (R * DPT < a.D) R <<= 1;
+    if (R > 32) return GL_ERR_SHAPE;
+    const int CT = MS_THREADS / R;
+    // tokens staged at a time: as many as 40 KB hold, at most 32 (a chunk costs a round trip to memory and
+    // three block-wide waits, which a few tokens do not pay for)
+    const int per_token = (2 * a.D + CT + 5) * (int)sizeof(float);
+    int CH = (40 * 1024) / per_token;
+    CH = CH > 32 ? 32 : CH;
+    if (CH < 1) return GL_ERR_SMEM;
+    const size_t smem = (size_t)CH * per_token;
+    const dim3 grid((a.V + CT - 1) / CT, a.H, a.B);
+    if (a.kind == 0) return gl_launch(memory_scan_kernel<TA, DPT, 0>, grid, dim3(MS_THREADS), smem, stream, 1, a, R, CH);
+    return gl_launch(memory_scan_kernel<TA, DPT, 1>, grid, dim3(MS_THREADS), smem, stream, 1, a, R, CH);
 }
 
-// blocks of columns a head of these sizes is spread over; the state row's size follows from it
-GL_API int gl_memory_scan_tiles(int D, int V) {
-    if (D <= 0 || V <= 0 || D > 512) return GL_ERR_SHAPE;
-    const int CT = RC_THREADS / memory_scan_lanes(D);
-    return (V + CT - 1) / CT;
+static int memory_scan_blocks(const MemoryScanArgs& a, int dpt) {
+    int R = 1;
+    while (R * dpt < a.D) R <<= 1;
+    if (R > 32) return -1;
+    const int CT = MS_THREADS / R;
+    return ((a.V + CT - 1) / CT) * a.H * a.B;
+}
+
+template <typename TA>
+static int dispatch_memory_scan(const MemoryScanArgs& a, cudaStream_t stream) {
+    // A thread walks the run's tokens one after the other, so the time of a long run is set by how little
+    // each thread does per token and by how many warps an SM has to switch between: rows of a column are
+    // spread over more lanes (fewer rows a thread) until the grid gives every SM several blocks.  With many
+    // sequences of one token the widest threads do, and fewer blocks re-read the tokens' q and k.
+    static int sms = 0;
+    if (!sms) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        if (sms <= 0) sms = 148;
+    }
+    const int want = 4 * sms;
+    const int b32 = memory_scan_blocks(a, 32), b8 = memory_scan_blocks(a, 8), b4 = memory_scan_blocks(a, 4);
+    int rc;
+    if (b32 >= want || (b8 < 0 && b4 < 0)) rc = launch_memory_scan<TA, 32>(a, stream);
+    else if (b8 >= want || b4 < 0) rc = b8 >= 0 ? launch_memory_scan<TA, 8>(a, stream) : launch_memory_scan<TA, 32>(a, stream);
+    else rc = launch_memory_scan<TA, 4>(a, stream);
+    if (rc != 0 || a.kind != 0) return rc;
+    return gl_launch(memory_commit_kernel, dim3(a.H, a.B), dim3(128), 0, stream, 1, a) == 0 ? GL_OK : GL_ERR_LAUNCH;
 }
 
 GL_API int gl_memory_scan(const MemoryScanArgs* args, int act_dtype, cudaStream_t stream) {
@@ -205,20 +253,10 @@ GL_API int gl_memory_scan(const MemoryScanArgs* args, int act_dtype, cudaStream_
     if (a.B <= 0) return GL_OK;
     if (a.H <= 0 || a.D <= 0 || a.V <= 0 || a.D > 512 || a.B > 65535 || a.H > 65535) return GL_ERR_SHAPE;
     if (a.kind != 0 && a.kind != 1) return GL_ERR_SHAPE;
-    if (a.kind == 0 && !(a.cap > 0.f)) return GL_ERR_SHAPE;
-    const int dpt = a.D <= 64 ? 8 : 32;
-    const int R = memory_scan_lanes(a.D);
-    if (R > 32) return GL_ERR_SHAPE;
-    {
-        const int tiles = gl_memory_scan_tiles(a.D, a.V);
-        const long long need = (long long)a.H * a.D * a.V + (a.kind == 0 ? (long long)a.H * tiles * (a.D + 1) : 0);
-        if (a.state_stride < need) return GL_ERR_SHAPE;
-    }
-    if (act_dtype == GL_F32)
-        return dpt == 8 ? launch_memory_scan<float, 8>(a, R, stream) : launch_memory_scan<float, 32>(a, R, stream);
-    if (act_dtype == GL_BF16)
-        return dpt == 8 ? launch_memory_scan<__nv_bfloat16, 8>(a, R, stream)
-                        : launch_memory_scan<__nv_bfloat16, 32>(a, R, stream);
+    if (a.kind == 0 && (!(a.cap > 0.f) || !a.nm_next)) return GL_ERR_SHAPE;
+    if (a.state_stride < (long long)a.H * a.D * a.V + (a.kind == 0 ? (long long)a.H * (a.D + 1) : 0)) return GL_ERR_SHAPE;
+    if (act_dtype == GL_F32) return dispatch_memory_scan<float>(a, stream);
+    if (act_dtype == GL_BF16) return dispatch_memory_scan<__nv_bfloat16>(a, stream);
     return GL_ERR_DTYPE;
 }
 
@@ -344,7 +382,8 @@ GL_API int gl_conv_silu(const ConvArgs* args, int act_dtype, cudaStream_t stream
 // Selective scan.  Per channel c and state n:
 //   dt = softplus(dtp[t, c]);  S[c, n] <- e^(dt A[c, n]) S[c, n] + dt x[t, c] B[t, n],  A = -e^(A_log)
 //   y[t, c] = (sum_n S[c, n] C[t, n] + D[c] x[t, c]) * silu(z[t, c])
-// A channel's states are spread over G adjacent lanes, up to 8 states a lane.
+// A channel's states are spread over G adjacent lanes, NPT states a lane (fewer states a lane and more lanes
+// when the grid would otherwise leave the SMs with a warp or two each: a thread walks the tokens in order).
 // ---------------------------------------------------------------------------
 struct SelectiveScanArgs {
     const void* x;            // [T, C] activation type (the convolution's output)
@@ -361,9 +400,7 @@ struct SelectiveScanArgs {
     int B, C, N, z_ld, z_off, state_stride;
 };
 
-#define SS_NPT 8
-
-template <typename TA>
+template <typename TA, int SS_NPT>
 __global__ void __launch_bounds__(RC_THREADS)
 selective_scan_kernel(SelectiveScanArgs a, int G) {
     extern __shared__ float smem[];
@@ -377,10 +414,10 @@ selective_scan_kernel(SelectiveScanArgs a, int G) {
     const bool live = c < C;
     const int qlen = a.seq_qlen[b], qstart = a.seq_qstart[b];
     float* Bs = smem;                                 // [CHUNK][N]
-    float* Cs = Bs + RC_CHUNK * N;                    // [CHUNK][N]
-    float* ds = Cs + RC_CHUNK * N;                    // [CHUNK][CPB] step sizes
-    float* xs = ds + RC_CHUNK * CPB;                  // [CHUNK][CPB]
-    float* zs = xs + RC_CHUNK * CPB;                  // [CHUNK][CPB]
+    float* Cs = Bs + SS_CHUNK * N;                    // [CHUNK][N]
+    float* ds = Cs + SS_CHUNK * N;                    // [CHUNK][CPB] step sizes
+    float* xs = ds + SS_CHUNK * CPB;                  // [CHUNK][CPB]
+    float* zs = xs + SS_CHUNK * CPB;                  // [CHUNK][CPB]
     float* S_g = a.state + (size_t)a.seq_slot[b] * a.state_stride + (size_t)(live ? c : 0) * N;
     float S[SS_NPT], A[SS_NPT];
 #pragma unroll
@@ -391,8 +428,8 @@ selective_scan_kernel(SelectiveScanArgs a, int G) {
         A[i] = ok ? -expf(a.a_log[(size_t)c * N + n]) : 0.f;
     }
     const float dskip = live ? a.d_skip[c] : 0.f;
-    for (int s0 = 0; s0 < qlen; s0 += RC_CHUNK) {
-        const int ns = min(RC_CHUNK, qlen - s0);
+    for (int s0 = 0; s0 < qlen; s0 += SS_CHUNK) {
+        const int ns = min(SS_CHUNK, qlen - s0);
         __syncthreads();
         for (int e = threadIdx.x; e < ns * N; e += RC_THREADS) {
             const int s = e / N, n = e - s * N;
@@ -409,6 +446,7 @@ selective_scan_kernel(SelectiveScanArgs a, int G) {
             zs[e] = ok ? gl_load((const TA*)a.z + t * a.z_ld + a.z_off + c0 + j) : 0.f;
         }
         __syncthreads();
+#pragma unroll 4
         for (int s = 0; s < ns; ++s) {
             const float dt = ds[s * CPB + cl], x = xs[s * CPB + cl];
             const float dx = dt * x;
@@ -439,17 +477,47 @@ selective_scan_kernel(SelectiveScanArgs a, int G) {
     }
 }
 
+template <typename TA, int NPT>
+static int launch_selective_scan(const SelectiveScanArgs& a, cudaStream_t stream) {
+    int G = 1;
+    while (G * NPT < a.N) G <<= 1;
+    if (G > 32) return GL_ERR_SHAPE;
+    const int CPB = RC_THREADS / G;
+    const size_t smem = (size_t)SS_CHUNK * (2 * a.N + 3 * CPB) * sizeof(float);
+    if (smem > 48 * 1024) return GL_ERR_SMEM;
+    const dim3 grid((a.C + CPB - 1) / CPB, a.B);
+    return gl_launch(selective_scan_kernel<TA, NPT>, grid, dim3(RC_THREADS), smem, stream, 1, a, G);
+}
+
+static int selective_scan_blocks(const SelectiveScanArgs& a, int npt) {
+    int G = 1;
+    while (G * npt < a.N) G <<= 1;
+    if (G > 32) return -1;
+    const int CPB = RC_THREADS / G;
+    return ((a.C + CPB - 1) / CPB) * a.B;
+}
+
+template <typename TA>
+static int dispatch_selective_scan(const SelectiveScanArgs& a, cudaStream_t stream) {
+    static int sms = 0;
+    if (!sms) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        if (sms <= 0) sms = 148;
+    }
+    const int want = 4 * sms;
+    const int b8 = selective_scan_blocks(a, 8), b2 = selective_scan_blocks(a, 2), b1 = selective_scan_blocks(a, 1);
+    if (b8 >= want || (b2 < 0 && b1 < 0)) return launch_selective_scan<TA, 8>(a, stream);
+    if (b2 >= want || b1 < 0) return b2 >= 0 ? launch_selective_scan<TA, 2>(a, stream) : launch_selective_scan<TA, 8>(a, stream);
+    return launch_selective_scan<TA, 1>(a, stream);
+}
+
 GL_API int gl_selective_scan(const SelectiveScanArgs* args, int act_dtype, cudaStream_t stream) {
     const SelectiveScanArgs& a = *args;
     if (a.B <= 0) return GL_OK;
-    if (a.C <= 0 || a.N <= 0 || a.N > 32 * SS_NPT || a.B > 65535) return GL_ERR_SHAPE;
-    int G = 1;
-    while (G * SS_NPT < a.N) G <<= 1;
-    const int CPB = RC_THREADS / G;
-    const size_t smem = (size_t)RC_CHUNK * (2 * a.N + 3 * CPB) * sizeof(float);
-    const dim3 grid((a.C + CPB - 1) / CPB, a.B);
-    if (act_dtype == GL_F32) return gl_launch(selective_scan_kernel<float>, grid, dim3(RC_THREADS), smem, stream, 1, a, G);
-    if (act_dtype == GL_BF16)
-        return gl_launch(selective_scan_kernel<__nv_bfloat16>, grid, dim3(RC_THREADS), smem, stream, 1, a, G);
+    if (a.C <= 0 || a.N <= 0 || a.N > 256 || a.B > 65535) return GL_ERR_SHAPE;
+    if (act_dtype == GL_F32) return dispatch_selective_scan<float>(a, stream);
+    if (act_dtype == GL_BF16) return dispatch_selective_scan<__nv_bfloat16>(a, stream);
     return GL_ERR_DTYPE;
 }

@@ -367,21 +367,25 @@ GL_API int gl_enter_pass(float* x, const float* base, const float* table, int T,
 // ---------------------------------------------------------------------------
 // A branch's output normalised over the width and added: 
 //   out[t, :] = alpha * a[t, :] / sqrt(mean(a[t, :]^2) + eps) * w + add0[t, :] + add1[t, :] + add2[t, :]
-// (32-bit rows; the adds may be absent; out may be one of them).  One warp per row.
+// (32-bit rows; the adds may be absent; out may be one of them).  One block per row.
 // ---------------------------------------------------------------------------
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(256)
 rms_scale_add_kernel(const float* a, const float* __restrict__ w, const float* add0, const float* add1, const float* add2,
                      float* out, int R, int D, float eps, float alpha) {
+    __shared__ float red[8];
     gl_grid_launch_dependents();
     gl_grid_wait();
-    const int lane = threadIdx.x & 31;
-    const int r = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    if (r >= R) return;
+    const int r = blockIdx.x;
     const float* src = a + (size_t)r * D;
     float q = 0.f;
-    for (int d = lane; d < D; d += 32) { const float v = src[d]; q += v * v; }
-    const float inv = alpha / sqrtf(gl_warp_sum(q) / (float)D + eps);
-    for (int d = lane; d < D; d += 32) {
+    for (int d = threadIdx.x; d < D; d += blockDim.x) { const float v = src[d]; q += v * v; }
+    q = gl_warp_sum(q);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = q;
+    __syncthreads();
+    float tot = 0.f;
+    for (int i = 0; i < (int)(blockDim.x >> 5); ++i) tot += red[i];      // same order in every thread
+    const float inv = alpha / sqrtf(tot / (float)D + eps);
+    for (int d = threadIdx.x; d < D; d += blockDim.x) {
         float y = src[d] * inv * w[d];
         const size_t i = (size_t)r * D + d;
         if (add0) y += add0[i];
@@ -395,5 +399,6 @@ GL_API int gl_rms_scale_add(const float* a, const float* w, const float* add0, c
                             float* out, int R, int D, float eps, float alpha, cudaStream_t stream) {
     if (R <= 0) return GL_OK;
     if (D <= 0) return GL_ERR_SHAPE;
-    return gl_launch(rms_scale_add_kernel, dim3((unsigned)((R + 3) / 4)), dim3(128), 0, stream, 1, a, w, add0, add1, add2, out, R, D, eps, alpha);
+    const int threads = D >= 2048 ? 256 : (D >= 512 ? 128 : 64);
+    return gl_launch(rms_scale_add_kernel, dim3((unsigned)R), dim3(threads), 0, stream, 1, a, w, add0, add1, add2, out, R, D, eps, alpha);
 }

@@ -929,33 +929,18 @@ class _MemoryScanArgs(Structure):
                 ("seq_slot", c_void_p), ("seq_qstart", c_void_p), ("seq_qlen", c_void_p),
                 ("ld", c_int), ("q_off", c_int), ("k_off", c_int), ("v_off", c_int), ("i_off", c_int), ("f_off", c_int),
                 ("B", c_int), ("H", c_int), ("D", c_int), ("V", c_int), ("state_stride", c_int), ("kind", c_int),
-                ("cap", c_float), ("q_scale", c_float)]
+                ("cap", c_float), ("q_scale", c_float), ("nm_next", c_void_p)]
 
 
 MEMORY_GATED, MEMORY_BOUNDED_FORGET = 0, 1
-_SCAN_THREADS = 128
-
-
-def memory_scan_tiles(D: int, V: int) -> int:
-    """Blocks of columns the scan spreads a head's [D, V] memory over (the rule of gl_memory_scan_tiles,
-    restated so that a state row can be sized without a compiled library)."""
-    if not 0 < D <= 512 or V <= 0:
-        raise KernelError(f"memory_scan takes 1..512 rows a head, got {D}")
-    dpt = 8 if D <= 64 else 32
-    lanes = 1
-    while lanes * dpt < D:
-        lanes *= 2
-    ct = _SCAN_THREADS // lanes
-    return -(-V // ct)
 
 
 def memory_state_size(kind: int, H: int, D: int, V: int) -> int:
-    """Floats of a sequence's state row: S [H, D, V]; the gated kind adds a normaliser [D] and a running
-    maximum for each block of columns of each head."""
-    n = H * D * V
-    if kind == MEMORY_GATED:
-        n += H * memory_scan_tiles(D, V) * (D + 1)
-    return n
+    """Floats of a sequence's state row: S [H, D, V]; the gated kind adds a normaliser [H, D] and a running
+    maximum [H]."""
+    if not 0 < D <= 512 or V <= 0 or H <= 0:
+        raise KernelError(f"memory_scan takes 1..512 rows a head, got {D}")
+    return H * D * V + (H * (D + 1) if kind == MEMORY_GATED else 0)
 
 
 def memory_scan(kind: int, proj: torch.Tensor, state: torch.Tensor, ctx, H: int, D: int, V: int,
@@ -972,11 +957,14 @@ def memory_scan(kind: int, proj: torch.Tensor, state: torch.Tensor, ctx, H: int,
     if kind == MEMORY_BOUNDED_FORGET:
         _need(lower, "lower", torch.float32, (H * D,))
     out = empty((T, H * V), torch.float32, proj.device)
+    # the gated kind's new normaliser and maximum, moved into the state rows by a second kernel
+    nm = empty((ctx.n_seqs, H, D + 1), torch.float32, proj.device) if kind == MEMORY_GATED else None
     a = _MemoryScanArgs(proj.data_ptr(), out.data_ptr(), state.data_ptr(), _addr(lower),
                         ctx.seq_slot.data_ptr(), ctx.seq_qstart.data_ptr(), ctx.seq_qlen.data_ptr(),
-                        ld, q_off, k_off, v_off, i_off, f_off, ctx.n_seqs, H, D, V, state.shape[1], kind, cap, q_scale)
+                        ld, q_off, k_off, v_off, i_off, f_off, ctx.n_seqs, H, D, V, state.shape[1], kind, cap, q_scale,
+                        _addr(nm))
     fn = _lib("recurrent.cu").gl_memory_scan
-    _check(_launch(fn, byref(a), c_int(dtype_code(proj.dtype)), _stream()), "memory_scan")
+    _check(_launch(fn, byref(a), c_int(dtype_code(proj.dtype)), _stream()), "memory_scan", 2 if kind == MEMORY_GATED else 1)
     return out
 
 
