@@ -177,9 +177,10 @@ def inspect(path: str, list_metadata: bool, list_tensors: bool) -> int:
     from .config.registry import resolve_architecture
     from .weights.safetensors_io import index_folder
     raw = read_config_json(path)
-    declared = (raw.get("architectures") or [raw.get("model_type", "")])[0]
-    arch = resolve_architecture(declared) or resolve_architecture(raw.get("model_type", ""))
-    shown = declared if arch is None or declared == arch.name else f"{declared} (loads as {arch.name})"
+    declared = (raw.get("architectures") or [raw.get("model_type") or raw.get("architecture") or ""])[0]
+    arch = (resolve_architecture(declared) or resolve_architecture(raw.get("model_type", ""))
+            or resolve_architecture(str(raw.get("architecture", ""))))
+    shown = declared if arch is None or declared.lower() == arch.name else f"{declared} (loads as {arch.name})"
     entries = index_folder(path)
     print(f"file: {path}\nname: {raw.get('_name_or_path', '')}\narchitecture: {shown}\n"
           f"supported: {str(arch is not None).lower()}\nmetadata: {len(raw)}\ntensors: {len(entries)}")

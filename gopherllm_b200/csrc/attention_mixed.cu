@@ -24,6 +24,10 @@ struct MixedAttnArgs {
     const int* pages;         // [B, max_pages]
     int T, B, nH, nKV, hd, vd, max_pages, window, max_qlen;
     int n_pages;
+    // one token a sequence, the context cut into ``splits`` ranges of pages, a block each:
+    float* parts;             // [B, nH, nVal, splits, vd] sums not yet divided
+    float* ml;                // [B, nH, splits, 2] each range's maximum and sum
+    int splits, pages_per_split;
 };
 
 #define AM_ROWS 8
@@ -34,7 +38,6 @@ template <typename TA, typename TC, int NACC>
 __global__ void __launch_bounds__(AM_ROWS * 32)
 attn_pairs_kernel(MixedAttnArgs a) {
     extern __shared__ float smem[];
-    gl_grid_launch_dependents();
     gl_grid_wait();
     const int hd = a.hd, vd = a.vd, ks = hd + 1;
     float* Ks = smem;                       // [GL_PAGE][hd+1]
@@ -262,11 +265,13 @@ attn_group_decode_kernel(MixedAttnArgs a) {
     float* sc = qv + gq * hd;                           // [gq][GL_PAGE] scores, then weights
     float* corr = sc + gq * GL_PAGE;                    // [gq] rescaling of this page, then 1 / sum
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int b = blockIdx.y, kh = blockIdx.x;
+    const int b = blockIdx.y, kh = blockIdx.x, split = blockIdx.z;
     const int nVal = a.mix ? a.nKV : 1;
     const int p = a.seq_ctx[b];
     const int lo = (a.window > 0 && p - a.window + 1 > 0) ? p - a.window + 1 : 0;
     const int row = a.seq_qstart[b];
+    const int page_first = lo / GL_PAGE + split * a.pages_per_split;
+    const int page_last = min(p / GL_PAGE, page_first + a.pages_per_split - 1);      // may lie before page_first: nothing to do
     const TA* qsrc = (const TA*)a.q + ((size_t)row * a.nH + (size_t)kh * gq) * hd;
     for (int i = threadIdx.x; i < gq * hd; i += AM_GTHREADS) qv[i] = gl_load(qsrc + i);
     const int vh = a.mix ? warp : kh;                   // this warp's value head
@@ -278,7 +283,7 @@ attn_group_decode_kernel(MixedAttnArgs a) {
         for (int i = 0; i < NACC; ++i) acc[g][i] = 0.f;
     float m = -INFINITY, l = 0.f;                       // warp g < gq keeps head g's running maximum and sum
     const int* pg = a.pages + (size_t)b * a.max_pages;
-    for (int page_i = lo / GL_PAGE; page_i <= p / GL_PAGE; ++page_i) {
+    for (int page_i = page_first; page_i <= page_last; ++page_i) {
         const int page = gl_checked(pg[gl_checked(page_i, a.max_pages, GL_BAD_POSITION)], a.n_pages > 0 ? a.n_pages : 0x7fffffff, GL_BAD_PAGE);
         const TC* kp = (const TC*)a.k_cache + ((size_t)page * a.nKV + kh) * GL_PAGE * hd;
         const int j0 = page_i * GL_PAGE;
@@ -340,21 +345,63 @@ attn_group_decode_kernel(MixedAttnArgs a) {
             }
         }
     }
-    __syncthreads();
-    if (warp < gq && lane == 0) corr[warp] = l > 0.f ? 1.0f / l : 0.f;
-    __syncthreads();
+    // the range's sums as they are, with its maximum and sum: the mixing kernel puts the ranges together
+    if (warp < gq && lane == 0) {
+        float* dst = a.ml + (((size_t)b * a.nH + (size_t)kh * gq + warp) * a.splits + split) * 2;
+        dst[0] = m;
+        dst[1] = l;
+    }
     if (has_values) {
 #pragma unroll
         for (int g = 0; g < GQ; ++g) {
             if (g < gq) {
-                float* o = a.pairs + (((size_t)row * a.nH + (size_t)kh * gq + g) * nVal + (a.mix ? vh : 0)) * vd;
+                float* o = a.parts + ((((size_t)b * a.nH + (size_t)kh * gq + g) * nVal + (a.mix ? vh : 0)) * a.splits + split) * vd;
 #pragma unroll
                 for (int i = 0; i < NACC; ++i) {
                     const int d = lane + 32 * i;
-                    if (d < vd) o[d] = acc[g][i] * corr[g];
+                    if (d < vd) o[d] = acc[g][i];
                 }
             }
         }
+    }
+}
+
+// out[b, h, :] = sum_g M[h, g] * (sum_s parts[b, g, c(h), s, :] e^(m_gs - m_g)) / (sum_s l_gs e^(m_gs - m_g))
+template <typename TA>
+__global__ void __launch_bounds__(128)
+head_mix_split_kernel(MixedAttnArgs a) {
+    extern __shared__ float coef[];                     // [heads taken][splits]: M[h, g] e^(m_gs - m_g) / sum_g
+    gl_grid_launch_dependents();
+    gl_grid_wait();
+    const int b = blockIdx.y, h = blockIdx.x;
+    const int nVal = a.mix ? a.nKV : 1;
+    const int c = a.mix ? h / (a.nH / a.nKV) : 0;
+    const int row = a.seq_qstart[b];
+    const int g0 = a.mix ? 0 : h, ng = a.mix ? a.nH : 1;
+    for (int gi = threadIdx.x; gi < ng; gi += blockDim.x) {
+        const int g = g0 + gi;
+        const float* ml = a.ml + ((size_t)b * a.nH + g) * a.splits * 2;
+        float mm = -INFINITY;
+        for (int s = 0; s < a.splits; ++s) mm = fmaxf(mm, ml[2 * s]);
+        float den = 0.f;
+        for (int s = 0; s < a.splits; ++s) {
+            const float e = ml[2 * s] > -INFINITY ? expf(ml[2 * s] - mm) : 0.f;
+            coef[gi * a.splits + s] = e;
+            den = fmaf(ml[2 * s + 1], e, den);
+        }
+        const float w = (a.mix ? a.mix[h * a.nH + g] : 1.0f) * (den > 0.f ? 1.0f / den : 0.f);
+        for (int s = 0; s < a.splits; ++s) coef[gi * a.splits + s] *= w;
+    }
+    __syncthreads();
+    const int terms = ng * a.splits;
+    for (int d = threadIdx.x; d < a.vd; d += blockDim.x) {
+        float y = 0.f;
+#pragma unroll 8
+        for (int i = 0; i < terms; ++i) {
+            const int gi = i / a.splits, s = i - gi * a.splits;
+            y = fmaf(coef[i], a.parts[((((size_t)b * a.nH + g0 + gi) * nVal + c) * a.splits + s) * a.vd + d], y);
+        }
+        gl_store((TA*)a.out + ((size_t)row * a.nH + h) * a.vd + d, y);
     }
 }
 
@@ -362,7 +409,7 @@ template <typename TA, typename TC, int NACC>
 static int launch_group_decode(const MixedAttnArgs& a, cudaStream_t stream) {
     const int gq = a.nH / a.nKV;
     const size_t smem = ((size_t)gq * a.hd + (size_t)gq * GL_PAGE + gq) * sizeof(float);
-    const dim3 grid(a.nKV, a.B);
+    const dim3 grid(a.nKV, a.B, a.splits);
     if (gq <= 1) return gl_launch(attn_group_decode_kernel<TA, TC, NACC, 1>, grid, dim3(AM_GTHREADS), smem, stream, 1, a);
     if (gq <= 2) return gl_launch(attn_group_decode_kernel<TA, TC, NACC, 2>, grid, dim3(AM_GTHREADS), smem, stream, 1, a);
     if (gq <= 4) return gl_launch(attn_group_decode_kernel<TA, TC, NACC, 4>, grid, dim3(AM_GTHREADS), smem, stream, 1, a);
@@ -397,8 +444,10 @@ template <typename TA, typename TC, int NACC>
 static int launch_mixed(const MixedAttnArgs& a, cudaStream_t stream) {
     const int pairs = a.nH * (a.mix ? a.nKV : 1);
     int rc;
-    if (a.max_qlen == 1 && a.nH / a.nKV <= 8 && a.nKV <= AM_GTHREADS / 32 && NACC <= 4) {
+    if (a.max_qlen == 1 && a.nH / a.nKV <= 8 && a.nKV <= AM_GTHREADS / 32 && NACC <= 4 && a.parts && a.ml && a.splits > 0) {
         rc = launch_group_decode<TA, TC, NACC>(a, stream);
+        if (rc != 0) return rc;
+        return gl_launch(head_mix_split_kernel<TA>, dim3(a.nH, a.B), dim3(a.vd <= 64 ? 64 : 128), (size_t)(a.mix ? a.nH : 1) * a.splits * sizeof(float), stream, 1, a);
     } else if (a.max_qlen == 1) {
         const size_t smem = ((size_t)a.hd + (size_t)AM_DWARPS * (a.vd + 2)) * sizeof(float);
         rc = gl_launch(attn_pairs_decode_kernel<TA, TC, NACC>, dim3(pairs, a.B), dim3(AM_DWARPS * 32), smem, stream, 1, a);

@@ -85,8 +85,7 @@ attn_pairs_tc_kernel(PairsArgs a) {
     const unsigned sQ = ap_smem(smem);
     const unsigned sK[2] = {sQ + AP_TILE, sQ + 2 * AP_TILE};
     const unsigned sV[2] = {sQ + 3 * AP_TILE, sQ + 3 * AP_TILE + AP_VTILE};
-    gl_grid_launch_dependents();
-    gl_grid_wait();
+    gl_grid_wait();                                            // (a long kernel: the next one is not launched early)
     const int b = blockIdx.z;
     const int h = blockIdx.y / a.nVal;                         // query head
     const int g = h / (a.nH / a.nKV);                          // its key head

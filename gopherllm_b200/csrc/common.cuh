@@ -48,6 +48,21 @@ __device__ __forceinline__ void gl_grid_launch_dependents() { asm volatile("grid
 
 template <typename... KArgs, typename... Args>
 static int gl_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                     int cluster_x, Args... args);
+
+// The same launch without the early start.  For a long kernel of few blocks: started early, its blocks are
+// placed on whichever SMs have room beside the kernel before, several to an SM, and stay there.
+template <typename... KArgs, typename... Args>
+static int gl_launch_in_order(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+    const int keep = gl_pdl;
+    gl_pdl = 0;
+    const int rc = gl_launch(kernel, grid, block, smem, stream, 1, args...);
+    gl_pdl = keep;
+    return rc;
+}
+
+template <typename... KArgs, typename... Args>
+static int gl_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
                      int cluster_x, Args... args) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;

@@ -253,10 +253,10 @@ struct QkvRowNormArgs {
 };
 
 template <typename TA, typename TC>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(512)
 qkv_rownorm_cache_kernel(QkvRowNormArgs a) {
     extern __shared__ float smem[];
-    __shared__ float red[4];
+    __shared__ float red[16];
     gl_grid_launch_dependents();
     gl_grid_wait();
     const int t = blockIdx.x;
@@ -272,15 +272,18 @@ qkv_rownorm_cache_kernel(QkvRowNormArgs a) {
     const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
     float inv_q = 1.f, inv_k = 1.f;
     {
+        const int nw = blockDim.x >> 5;
         sq = gl_warp_sum(sq);
         if (lane == 0) red[w] = sq;
         __syncthreads();
-        const float tq = (red[0] + red[1]) + (red[2] + red[3]);
+        float tq = 0.f;
+        for (int i = 0; i < nw; ++i) tq += red[i];           // same order in every thread
         __syncthreads();
         sk = gl_warp_sum(sk);
         if (lane == 0) red[w] = sk;
         __syncthreads();
-        const float tk = (red[0] + red[1]) + (red[2] + red[3]);
+        float tk = 0.f;
+        for (int i = 0; i < nw; ++i) tk += red[i];
         if (a.q_gamma) inv_q = 1.0f / sqrtf(tq / (float)nq + a.eps);
         if (a.k_gamma) inv_k = 1.0f / sqrtf(tk / (float)nk + a.eps);
     }
@@ -328,7 +331,8 @@ GL_API int gl_qkv_rownorm_cache(const QkvRowNormArgs* args, int act_dtype, int c
     if (a.hd <= 0 || a.vd <= 0 || a.nH <= 0 || a.nKV <= 0 || 2 * a.half > a.hd) return GL_ERR_SHAPE;
     const size_t smem = (size_t)(a.nH + a.nKV) * a.hd * sizeof(float);
     if (smem > 48 * 1024) return GL_ERR_SMEM;
-    const dim3 g((unsigned)a.T), b(128);
+    // few tokens: more threads a token, so that a row's loads are in flight together
+    const dim3 g((unsigned)a.T), b(a.T <= 256 && (a.nH + a.nKV) * a.hd >= 2048 ? 512 : 128);
     if (act_dtype == GL_F32 && cache_dtype == GL_F32) return gl_launch(qkv_rownorm_cache_kernel<float, float>, g, b, smem, stream, 1, a);
     if (act_dtype == GL_BF16 && cache_dtype == GL_BF16)
         return gl_launch(qkv_rownorm_cache_kernel<__nv_bfloat16, __nv_bfloat16>, g, b, smem, stream, 1, a);

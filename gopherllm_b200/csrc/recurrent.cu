@@ -27,6 +27,19 @@ __device__ __forceinline__ float rc_softplus(float x) { return x > 20.0f ? x : l
 // rounded once; expf's last-bit errors near one do not average out over a thousand tokens of a slowly
 // decaying state.
 __device__ __forceinline__ float rc_decay(float x) {
+    if (x > -0.5f && x <= 0.f) {
+        // 1 + (e^x - 1) with e^x - 1 from its series to x^9/9! (below 2^-28 here), Horner in 32-bit
+        float p = 2.755731922e-6f;
+        p = fmaf(p, x, 2.48015873e-5f);
+        p = fmaf(p, x, 1.984126984e-4f);
+        p = fmaf(p, x, 1.388888889e-3f);
+        p = fmaf(p, x, 8.333333333e-3f);
+        p = fmaf(p, x, 4.166666667e-2f);
+        p = fmaf(p, x, 1.666666667e-1f);
+        p = fmaf(p, x, 0.5f);
+        p = fmaf(p, x, 1.0f);
+        return fmaf(p, x, 1.0f);
+    }
     if (x > -0.5f) return 1.0f + expm1f(x);
     return expf(x);
 }
@@ -56,11 +69,14 @@ struct MemoryScanArgs {
     float* nm_next;           // kind 0: [B, H, D + 1] scratch for the new normaliser and maximum
 };
 
-template <typename TA, int DPT, int KIND>
+// FULL: D == R * DPT and D a multiple of 4, so a thread's rows are DPT consecutive ones read as float4 and no
+// row needs a bounds check.
+template <typename TA, int DPT, int KIND, bool FULL>
 __global__ void __launch_bounds__(MS_THREADS)
 memory_scan_kernel(MemoryScanArgs a, int R, int CH) {
-    extern __shared__ float smem[];
-    gl_grid_launch_dependents();
+    extern __shared__ __align__(16) float smem[];
+    // (launched in order, not early: placed beside the kernel before, the blocks of a scan sat several to an SM
+    // for its whole length, and a prompt of 2,048 tokens took 25 ms instead of 16)
     gl_grid_wait();
     const int D = a.D, V = a.V, H = a.H;
     const int CT = MS_THREADS / R;                    // columns of a block
@@ -82,7 +98,7 @@ memory_scan_kernel(MemoryScanArgs a, int R, int CH) {
     float S[DPT], n[DPT];
 #pragma unroll
     for (int i = 0; i < DPT; ++i) {
-        const int d = r + R * i;
+        const int d = FULL ? r * DPT + i : r + R * i;
         S[i] = (live && d < D) ? S_g[(size_t)d * V + col] : 0.f;
         n[i] = (KIND == 0 && d < D) ? n_g[d] : 0.f;
     }
@@ -142,28 +158,38 @@ memory_scan_kernel(MemoryScanArgs a, int R, int CH) {
             const float* k = ks + s * D;
             const float v = vs[s * CT + c];
             float num = 0.f, nq = 0.f;
-            if (KIND == 0) {
-                const float keep = gs[s * 4 + 2], take = gs[s * 4 + 3];
+            float qr[DPT], kr[DPT];
+            if (FULL) {
 #pragma unroll
-                for (int i = 0; i < DPT; ++i) {
-                    const int d = r + R * i;
-                    if (d < D) {
-                        const float kk = take * k[d];
-                        S[i] = fmaf(keep, S[i], kk * v);
-                        n[i] = fmaf(keep, n[i], kk);
-                        num = fmaf(S[i], q[d], num);
-                        nq = fmaf(n[i], q[d], nq);
-                    }
+                for (int i = 0; i < DPT; i += 4) {
+                    const float4 q4 = *(const float4*)(q + r * DPT + i), k4 = *(const float4*)(k + r * DPT + i);
+                    qr[i] = q4.x; qr[i + 1] = q4.y; qr[i + 2] = q4.z; qr[i + 3] = q4.w;
+                    kr[i] = k4.x; kr[i + 1] = k4.y; kr[i + 2] = k4.z; kr[i + 3] = k4.w;
                 }
             } else {
 #pragma unroll
                 for (int i = 0; i < DPT; ++i) {
                     const int d = r + R * i;
-                    if (d < D) {
-                        const float f = k[d];
-                        S[i] = fmaf(f, S[i], (1.0f - f) * v);
-                        num = fmaf(S[i], q[d], num);
-                    }
+                    qr[i] = d < D ? q[d] : 0.f;
+                    kr[i] = d < D ? k[d] : (KIND == 0 ? 0.f : 1.f);      // a row that does not exist keeps its zero
+                }
+            }
+            if (KIND == 0) {
+                const float keep = gs[s * 4 + 2], take = gs[s * 4 + 3];
+                const float tv = take * v;
+#pragma unroll
+                for (int i = 0; i < DPT; ++i) {
+                    S[i] = fmaf(keep, S[i], kr[i] * tv);
+                    n[i] = fmaf(keep, n[i], take * kr[i]);
+                    num = fmaf(S[i], qr[i], num);
+                    nq = fmaf(n[i], qr[i], nq);
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < DPT; ++i) {
+                    const float f = kr[i];
+                    S[i] = fmaf(f, S[i], (1.0f - f) * v);
+                    num = fmaf(S[i], qr[i], num);
                 }
             }
             for (int o = R >> 1; o > 0; o >>= 1) {
@@ -179,7 +205,7 @@ memory_scan_kernel(MemoryScanArgs a, int R, int CH) {
     }
 #pragma unroll
     for (int i = 0; i < DPT; ++i) {
-        const int d = r + R * i;
+        const int d = FULL ? r * DPT + i : r + R * i;
         if (d < D) {
             if (live) S_g[(size_t)d * V + col] = S[i];
             if (KIND == 0 && blockIdx.x == 0 && c == 0) a.nm_next[((size_t)b * H + h) * (D + 1) + d] = n[i];
@@ -213,8 +239,13 @@ static int launch_memory_scan(const MemoryScanArgs& a, cudaStream_t stream) {
     if (CH < 1) return GL_ERR_SMEM;
     const size_t smem = (size_t)CH * per_token;
     const dim3 grid((a.V + CT - 1) / CT, a.H, a.B);
-    if (a.kind == 0) return gl_launch(memory_scan_kernel<TA, DPT, 0>, grid, dim3(MS_THREADS), smem, stream, 1, a, R, CH);
-    return gl_launch(memory_scan_kernel<TA, DPT, 1>, grid, dim3(MS_THREADS), smem, stream, 1, a, R, CH);
+    const bool full = DPT >= 4 && a.D == R * DPT;
+    if (a.kind == 0) {
+        if (full) return gl_launch_in_order(memory_scan_kernel<TA, DPT, 0, true>, grid, dim3(MS_THREADS), smem, stream, a, R, CH);
+        return gl_launch_in_order(memory_scan_kernel<TA, DPT, 0, false>, grid, dim3(MS_THREADS), smem, stream, a, R, CH);
+    }
+    if (full) return gl_launch_in_order(memory_scan_kernel<TA, DPT, 1, true>, grid, dim3(MS_THREADS), smem, stream, a, R, CH);
+    return gl_launch_in_order(memory_scan_kernel<TA, DPT, 1, false>, grid, dim3(MS_THREADS), smem, stream, a, R, CH);
 }
 
 static int memory_scan_blocks(const MemoryScanArgs& a, int dpt) {
@@ -404,7 +435,8 @@ template <typename TA, int SS_NPT>
 __global__ void __launch_bounds__(RC_THREADS)
 selective_scan_kernel(SelectiveScanArgs a, int G) {
     extern __shared__ float smem[];
-    gl_grid_launch_dependents();
+    // (launched in order, not early: placed beside the kernel before, the blocks of a scan sat several to an SM
+    // for its whole length, and a prompt of 2,048 tokens took 25 ms instead of 16)
     gl_grid_wait();
     const int N = a.N, C = a.C;
     const int CPB = RC_THREADS / G;
@@ -486,7 +518,7 @@ static int launch_selective_scan(const SelectiveScanArgs& a, cudaStream_t stream
     const size_t smem = (size_t)SS_CHUNK * (2 * a.N + 3 * CPB) * sizeof(float);
     if (smem > 48 * 1024) return GL_ERR_SMEM;
     const dim3 grid((a.C + CPB - 1) / CPB, a.B);
-    return gl_launch(selective_scan_kernel<TA, NPT>, grid, dim3(RC_THREADS), smem, stream, 1, a, G);
+    return gl_launch_in_order(selective_scan_kernel<TA, NPT>, grid, dim3(RC_THREADS), smem, stream, a, G);
 }
 
 static int selective_scan_blocks(const SelectiveScanArgs& a, int npt) {

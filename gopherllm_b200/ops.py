@@ -1102,7 +1102,16 @@ class _MixedAttnArgs(Structure):
     _fields_ = [("q", c_void_p), ("pairs", c_void_p), ("out", c_void_p), ("k_cache", c_void_p), ("v_cache", c_void_p),
                 ("mix", c_void_p), ("seq_qstart", c_void_p), ("seq_qlen", c_void_p), ("seq_ctx", c_void_p), ("pages", c_void_p),
                 ("T", c_int), ("B", c_int), ("nH", c_int), ("nKV", c_int), ("hd", c_int), ("vd", c_int),
-                ("max_pages", c_int), ("window", c_int), ("max_qlen", c_int), ("n_pages", c_int)]
+                ("max_pages", c_int), ("window", c_int), ("max_qlen", c_int), ("n_pages", c_int),
+                ("parts", c_void_p), ("ml", c_void_p), ("splits", c_int), ("pages_per_split", c_int)]
+
+
+def mixed_decode_splits(batch: int, num_kv_heads: int, max_len: int, device) -> int:
+    """Ranges of pages a sequence's context is cut into for a one-token step: enough blocks (key heads x
+    sequences x ranges) for about two an SM, no range shorter than a page."""
+    pages = max(1, -(-int(max_len) // PAGE))
+    want = max(1, (2 * sm_count(device)) // max(1, batch * num_kv_heads))
+    return max(1, min(pages, want, 64))
 
 
 class _PairsArgs(Structure):
@@ -1134,7 +1143,16 @@ def attention_mixed(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
     a = _MixedAttnArgs(q.data_ptr(), pairs.data_ptr(), out.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), _addr(mix),
                        ctx.seq_qstart.data_ptr(), ctx.seq_qlen.data_ptr(), ctx.seq_ctx.data_ptr(), pages.data_ptr(),
                        T, ctx.n_seqs, num_heads, num_kv_heads, head_dim, value_dim, pages.shape[-1], window,
-                       ctx.max_qlen, k_cache.shape[0])
+                       ctx.max_qlen, k_cache.shape[0], None, None, 0, 0)
+    if ctx.max_qlen == 1 and num_heads // num_kv_heads <= 8 and num_kv_heads <= 8 and value_dim <= 128:
+        # one token a sequence: the context in ranges of pages, a block each (sized for the step's longest
+        # sequence; a captured step is sized for its bucket's longest), put together by the mixing kernel
+        splits = mixed_decode_splits(ctx.n_seqs, num_kv_heads, ctx.max_len, q.device)
+        a.splits = splits
+        a.pages_per_split = -(-max(1, -(-int(ctx.max_len) // PAGE)) // splits)
+        parts = empty((ctx.n_seqs, num_heads, n_val, splits, value_dim), torch.float32, q.device)
+        ml = empty((ctx.n_seqs, num_heads, splits, 2), torch.float32, q.device)
+        a.parts, a.ml = parts.data_ptr(), ml.data_ptr()
     lib = _lib("attention_mixed.cu")
     if (USE_PAIRS_TC and ctx.max_qlen > 1 and q.dtype == torch.bfloat16 and k_cache.dtype == torch.bfloat16
             and head_dim % 16 == 0 and value_dim % 16 == 0 and not DEBUG_BOUNDS):

@@ -85,10 +85,26 @@ def test_trace_run(dtype):
         assert err <= bound, f"{dtype} step {s['step']} ({expect[s['step']][:3]}…): {err:.3e} > {bound:.3e}"
 
 
-def test_trace_run_refuses_more_tokens_than_the_cache_holds():
+def test_trace_run_refuses_a_sequence_the_cache_cannot_hold():
+    """--max-tokens counts tokens and the cache whole pages, so the runner leaves every live request a
+    page of slack; a sequence past the model's longest is still refused."""
     folder = tiny.folder("A")
-    steps = [{"step": 0, "entries": [{"id": "a", "tokens": [1] * 65, "want": [0]}], "end": []}]
+    longest = tiny.TINY_A["max_position_embeddings"]
+    steps = [{"step": 0, "entries": [{"id": "a", "tokens": [1] * (longest + 1), "want": [0]}], "end": []}]
     proc = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", folder,
                            "--dtype", "float32", "--out", tempfile.mkdtemp(), "--max-tokens", "64"],
                           input=json.dumps(steps[0]) + "\n", capture_output=True, text=True, timeout=600)
-    assert proc.returncode != 0 and "pages" in proc.stderr
+    assert proc.returncode != 0 and "positions" in proc.stderr
+
+
+def test_trace_run_holds_max_tokens_whatever_the_page_rounding():
+    """Three live requests of 22, 21 and 21 tokens are 64 tokens and three pages."""
+    folder = tiny.folder("A")
+    steps = [{"step": 0, "entries": [{"id": i, "tokens": [3 + i] * n, "want": [n - 1]} for i, n in enumerate((22, 21, 21))],
+              "end": [0, 1, 2]}]
+    out = tempfile.mkdtemp()
+    proc = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", folder,
+                           "--dtype", "float32", "--out", out, "--max-tokens", "64"],
+                          input=json.dumps(steps[0]) + "\n", capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    assert os.path.getsize(os.path.join(out, "0.f32")) == 3 * 4 * tiny.TINY_A["vocab_size"]

@@ -137,3 +137,22 @@ def test_plain_gated_memory_matches_its_closed_form():
     o = torch.stack(rows)
     want = pv.rms_norm(o, None, 1e-6) * torch.sigmoid(h @ t["g"].T)
     assert torch.allclose(got, want, atol=1e-9)
+
+
+def test_command_line_inspects_and_writes_a_random_folder(tmp_path, capsys):
+    """--random-config writes a Vopedra folder the loader's check accepts; --inspect names the design."""
+    import json
+    from gopherllm_b200.cli import main
+    cfg_file = tmp_path / "c.json"
+    cfg_file.write_text(json.dumps(vm.GAMMA))
+    folder = str(tmp_path / "m")
+    assert main([folder, "--random-config", str(cfg_file), "--seed", "3"]) == 0
+    arch, typed, model = build(vm.GAMMA)
+    check_folder(folder, tensor_table(model.parameters(), arch.tensor_names(typed)))
+    capsys.readouterr()
+    assert main([folder, "--inspect"]) == 0
+    out = capsys.readouterr().out
+    assert "architecture: Vopedra" in out and "supported: true" in out
+    _, t = pv.read_folder(folder)
+    logits = pv.forward(vm.GAMMA, t, [1, 2, 3, 4, 5])
+    assert torch.isfinite(logits).all()
