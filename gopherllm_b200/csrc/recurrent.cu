@@ -153,13 +153,14 @@ memory_scan_kernel(MemoryScanArgs a, int R, int CH) {
             }
         }
         __syncthreads();
+#pragma unroll 4
         for (int s = 0; s < ns; ++s) {
             const float* q = qs + s * D;
             const float* k = ks + s * D;
             const float v = vs[s * CT + c];
             float num = 0.f, nq = 0.f;
             float qr[DPT], kr[DPT];
-            if (FULL) {
+            if constexpr (FULL && DPT >= 4) {
 #pragma unroll
                 for (int i = 0; i < DPT; i += 4) {
                     const float4 q4 = *(const float4*)(q + r * DPT + i), k4 = *(const float4*)(k + r * DPT + i);
@@ -270,11 +271,23 @@ static int dispatch_memory_scan(const MemoryScanArgs& a, cudaStream_t stream) {
         if (sms <= 0) sms = 148;
     }
     const int want = 4 * sms;
-    const int b32 = memory_scan_blocks(a, 32), b8 = memory_scan_blocks(a, 8), b4 = memory_scan_blocks(a, 4);
+    const int dpts[5] = {32, 8, 4, 2, 1};
+    int pick = -1;
+    for (int i = 0; i < 5; ++i) {
+        const int blocks = memory_scan_blocks(a, dpts[i]);
+        if (blocks < 0) continue;
+        pick = dpts[i];                                  // the last that exists if none gives enough blocks
+        if (blocks >= want) break;
+    }
     int rc;
-    if (b32 >= want || (b8 < 0 && b4 < 0)) rc = launch_memory_scan<TA, 32>(a, stream);
-    else if (b8 >= want || b4 < 0) rc = b8 >= 0 ? launch_memory_scan<TA, 8>(a, stream) : launch_memory_scan<TA, 32>(a, stream);
-    else rc = launch_memory_scan<TA, 4>(a, stream);
+    switch (pick) {
+        case 32: rc = launch_memory_scan<TA, 32>(a, stream); break;
+        case 8: rc = launch_memory_scan<TA, 8>(a, stream); break;
+        case 4: rc = launch_memory_scan<TA, 4>(a, stream); break;
+        case 2: rc = launch_memory_scan<TA, 2>(a, stream); break;
+        case 1: rc = launch_memory_scan<TA, 1>(a, stream); break;
+        default: return GL_ERR_SHAPE;
+    }
     if (rc != 0 || a.kind != 0) return rc;
     return gl_launch(memory_commit_kernel, dim3(a.H, a.B), dim3(128), 0, stream, 1, a) == 0 ? GL_OK : GL_ERR_LAUNCH;
 }
@@ -459,7 +472,6 @@ selective_scan_kernel(SelectiveScanArgs a, int G) {
         S[i] = ok ? S_g[n] : 0.f;
         A[i] = ok ? -expf(a.a_log[(size_t)c * N + n]) : 0.f;
     }
-    const float dskip = live ? a.d_skip[c] : 0.f;
     for (int s0 = 0; s0 < qlen; s0 += SS_CHUNK) {
         const int ns = min(SS_CHUNK, qlen - s0);
         __syncthreads();
@@ -494,9 +506,15 @@ selective_scan_kernel(SelectiveScanArgs a, int G) {
                 }
             }
             for (int o = G >> 1; o > 0; o >>= 1) y += __shfl_xor_sync(0xffffffffu, y, o);
-            if (g == 0 && live) {
-                y = fmaf(dskip, x, y);
-                gl_store((TA*)a.out + (size_t)(qstart + s0 + s) * C + c, y * rc_silu(zs[s * CPB + cl]));
+            if (g == 0) ds[s * CPB + cl] = y;           // the step size has been used: its place takes the sum
+        }
+        __syncthreads();
+        // the skip connection and the gate do not go from token to token: all of the chunk's outputs at once
+        for (int e = threadIdx.x; e < ns * CPB; e += RC_THREADS) {
+            const int s = e / CPB, j = e - s * CPB;
+            if (c0 + j < C) {
+                const float y = fmaf(a.d_skip[c0 + j], xs[e], ds[e]);
+                gl_store((TA*)a.out + (size_t)(qstart + s0 + s) * C + c0 + j, y * rc_silu(zs[e]));
             }
         }
     }
