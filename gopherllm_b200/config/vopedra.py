@@ -101,7 +101,7 @@ class VopedraConfig:
             for k in ("start", "stop", "times"):
                 if isinstance(lp.get(k), bool) or not isinstance(lp.get(k), int):
                     raise ValueError(f"config.json: loop.{k} must be an integer")
-            if not (0 <= lp["start"] < lp["stop"] <= len(self.layers)) or lp["times"] < 1:
+            if not (0 <= lp["start"] <= lp["stop"] <= len(self.layers)) or lp["times"] < 1:
                 raise ValueError(f"config.json: loop {lp} does not fit {len(self.layers)} layers")
 
 

@@ -29,7 +29,7 @@ def test_architecture_is_found_by_its_plain_key():
         architecture_from_config({"architecture": "Nonesuch"})
 
 
-@pytest.mark.parametrize("cfg", [vm.ALPHA, vm.BETA, vm.GAMMA], ids=["alpha", "beta", "gamma"])
+@pytest.mark.parametrize("cfg", [vm.ALPHA, vm.BETA, vm.GAMMA, vm.DELTA], ids=["alpha", "beta", "gamma", "delta"])
 def test_declared_tensors_are_the_files_tensors(cfg):
     """The names and shapes the parts declare are the ones the tests write by the design's naming
     rules; a folder written that way passes the loader's check."""

@@ -88,7 +88,7 @@ def test_each_mechanism_alone(name, cfg, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("cfg_name", ["ALPHA", "BETA", "GAMMA"])
+@pytest.mark.parametrize("cfg_name", ["ALPHA", "BETA", "GAMMA", "DELTA"])
 def test_whole_pieces_and_single_tokens(cfg_name, dtype):
     """The same tokens whole, in pieces of many sizes down to two, and mostly one by one."""
     cfg = getattr(vm, cfg_name)

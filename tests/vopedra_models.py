@@ -6,8 +6,9 @@ name or shape on either side shows.  Sizes differ between the configurations in 
 widths, head counts (also one head, and as many key/value heads as query heads), key sizes above and
 below 64, value sizes other than key sizes, memories wider than one block of columns, states of more
 than eight entries a channel, a low rank that is no multiple of 8, filters of one to four taps, a
-rotation over the whole head, over a part and over nothing, a loop run once, three times and no loop,
-layers without a feed-forward.
+rotation over the whole head, over a part and over nothing, a loop run once, three times, over no layer
+and no loop, layers without a feed-forward, sizes that are multiples of nothing, more query heads a
+key/value head and more key/value heads than the fast one-token kernel takes.
 """
 import json
 import os
@@ -46,6 +47,22 @@ GAMMA = dict(
         {"type": "mlstm", "mixer": {"heads": 3, "dim": 8, "vdim": 8, "gate_cap": 6.0}, "mlp": {"kind": "dense", "ff": 24}},
     ],
     loop={"start": 0, "stop": 2, "times": 1})
+
+
+# sizes that are multiples of nothing convenient, nine query heads on one key/value head, an empty loop
+DELTA = dict(
+    architecture="Vopedra", vocab=91, width=36, norm={"eps": 3e-6},
+    layers=[
+        {"type": "parallel", "mixer": {
+            "left": {"heads": 9, "kv_heads": 1, "dim": 6, "vdim": 10, "rot": {"dims": 4, "base": 100.0}, "scale": 0.4},
+            "right": {"heads": 2, "dim": 5, "vdim": 7}}, "mlp": {"kind": "dense", "ff": 20}},
+        {"type": "mamba1", "mixer": {"inner": 10, "state": 3, "dt_rank": 2, "conv": 3}, "mlp": {"kind": "dense", "ff": 11}},
+        {"type": "mlstm", "mixer": {"heads": 3, "dim": 5, "vdim": 9, "gate_cap": 4.0}, "mlp": None},
+        {"type": "parallel", "mixer": {
+            "left": {"heads": 20, "kv_heads": 10, "dim": 16, "vdim": 16, "rot": {"dims": 16, "base": 300.0}, "scale": 0.25},
+            "right": {"heads": 1, "dim": 3, "vdim": 2}}, "mlp": None},
+    ],
+    loop={"start": 2, "stop": 2, "times": 2})
 
 
 def only(cfg, index, mlp=True, loop=None):
