@@ -121,10 +121,12 @@ def load(source: str, defines: Tuple[str, ...] = ()) -> ctypes.CDLL:
         return lib
 
 
-def build_all(head_dims: Iterable[int] = (), verbose: bool = True) -> None:
-    """Compile every library (the per-head-size ones for ``head_dims``), several at a time."""
+def build_all(head_dims: Iterable[int] = (), verbose: bool = True, pair_dims: Iterable[Tuple[int, int]] = ()) -> None:
+    """Compile every library (the per-head-size ones for ``head_dims``, the ones per key and value size for
+    ``pair_dims``), several at a time."""
     from . import catalog
     jobs = list(catalog.all_libraries(head_dims))
+    jobs += [(src, catalog.pair_dim_defines(hd, vd)) for src in catalog.PER_PAIR_DIMS for hd, vd in pair_dims]
     errors = []
 
     def work(job):

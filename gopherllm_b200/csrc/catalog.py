@@ -10,6 +10,8 @@ GENERAL = ("rowwise.cu", "qkv_cache.cu", "attention_generic.cu", "attention_mixe
 # libraries compiled once per head size (GL_HEAD_DIM)
 PER_HEAD_DIM: Tuple[str, ...] = ("attention_decode.cu", "attention_prefill.cu", "attention_prefill_tc.cu",
                                   "decode_layer.cu")
+# libraries compiled once per (key size, value size): GL_HEAD_DIM and, where it differs, GL_VALUE_DIM
+PER_PAIR_DIMS: Tuple[str, ...] = ("attention_mixed_tc.cu",)
 # libraries that take only some head sizes
 MAX_HEAD_DIM = {"attention_prefill_tc.cu": 128, "decode_layer.cu": 128}
 

@@ -442,9 +442,17 @@ struct SelectiveScanArgs {
     const int* seq_qstart;
     const int* seq_qlen;
     int B, C, N, z_ld, z_off, state_stride;
+    // a long run cut into chunks of chunk_len tokens that are walked side by side (n_chunks > 1):
+    //   first every chunk from a zero state, keeping its last state and the sum of its step sizes;
+    //   then a carry over the chunks, S_start[k+1] = e^(A sum_k) S_start[k] + last_k (the decays of a chunk
+    //   multiply to e^(A sum of its step sizes));  then every chunk again from its true start, with outputs.
+    float* chunk_state;       // [B, n_chunks, C, N]
+    float* chunk_dt;          // [B, n_chunks, C]
+    int chunk_len, n_chunks;
 };
 
-template <typename TA, int SS_NPT>
+// MODE 0: a run in one piece.  MODE 1: a chunk from a zero state, no outputs.  MODE 2: a chunk from its start.
+template <typename TA, int SS_NPT, int MODE>
 __global__ void __launch_bounds__(RC_THREADS)
 selective_scan_kernel(SelectiveScanArgs a, int G) {
     extern __shared__ float smem[];
@@ -458,22 +466,28 @@ selective_scan_kernel(SelectiveScanArgs a, int G) {
     const int c = c0 + cl;
     const bool live = c < C;
     const int qlen = a.seq_qlen[b], qstart = a.seq_qstart[b];
+    const int chunk = MODE == 0 ? 0 : blockIdx.z;
+    const int t_begin = MODE == 0 ? 0 : chunk * a.chunk_len;
+    const int t_end = MODE == 0 ? qlen : min(qlen, t_begin + a.chunk_len);
+    if (t_begin >= qlen) return;                      // (the whole block: this sequence has no such chunk)
     float* Bs = smem;                                 // [CHUNK][N]
     float* Cs = Bs + SS_CHUNK * N;                    // [CHUNK][N]
     float* ds = Cs + SS_CHUNK * N;                    // [CHUNK][CPB] step sizes
     float* xs = ds + SS_CHUNK * CPB;                  // [CHUNK][CPB]
     float* zs = xs + SS_CHUNK * CPB;                  // [CHUNK][CPB]
     float* S_g = a.state + (size_t)a.seq_slot[b] * a.state_stride + (size_t)(live ? c : 0) * N;
+    float* S_c = MODE == 0 ? S_g : a.chunk_state + (((size_t)b * a.n_chunks + chunk) * C + (live ? c : 0)) * N;
     float S[SS_NPT], A[SS_NPT];
 #pragma unroll
     for (int i = 0; i < SS_NPT; ++i) {
         const int n = g + G * i;
         const bool ok = live && n < N;
-        S[i] = ok ? S_g[n] : 0.f;
+        S[i] = (ok && MODE != 1) ? (MODE == 0 ? S_g[n] : S_c[n]) : 0.f;
         A[i] = ok ? -expf(a.a_log[(size_t)c * N + n]) : 0.f;
     }
-    for (int s0 = 0; s0 < qlen; s0 += SS_CHUNK) {
-        const int ns = min(SS_CHUNK, qlen - s0);
+    float dt_sum = 0.f;
+    for (int s0 = t_begin; s0 < t_end; s0 += SS_CHUNK) {
+        const int ns = min(SS_CHUNK, t_end - s0);
         __syncthreads();
         for (int e = threadIdx.x; e < ns * N; e += RC_THREADS) {
             const int s = e / N, n = e - s * N;
@@ -494,6 +508,7 @@ selective_scan_kernel(SelectiveScanArgs a, int G) {
         for (int s = 0; s < ns; ++s) {
             const float dt = ds[s * CPB + cl], x = xs[s * CPB + cl];
             const float dx = dt * x;
+            if (MODE == 1) dt_sum += dt;
             const float* Bt = Bs + s * N;
             const float* Ct = Cs + s * N;
             float y = 0.f;
@@ -508,6 +523,7 @@ selective_scan_kernel(SelectiveScanArgs a, int G) {
             for (int o = G >> 1; o > 0; o >>= 1) y += __shfl_xor_sync(0xffffffffu, y, o);
             if (g == 0) ds[s * CPB + cl] = y;           // the step size has been used: its place takes the sum
         }
+        if (MODE == 1) continue;
         __syncthreads();
         // the skip connection and the gate do not go from token to token: all of the chunk's outputs at once
         for (int e = threadIdx.x; e < ns * CPB; e += RC_THREADS) {
@@ -518,12 +534,34 @@ selective_scan_kernel(SelectiveScanArgs a, int G) {
             }
         }
     }
-    if (live) {
+    if (live && (MODE != 2 || t_end == qlen)) {       // the state row takes the run's last state
+        float* dst = MODE == 1 ? S_c : S_g;
 #pragma unroll
         for (int i = 0; i < SS_NPT; ++i) {
             const int n = g + G * i;
-            if (n < N) S_g[n] = S[i];
+            if (n < N) dst[n] = S[i];
         }
+    }
+    if (MODE == 1 && live && g == 0) a.chunk_dt[((size_t)b * a.n_chunks + chunk) * C + c] = dt_sum;
+}
+
+// Between the two walks: every chunk's start state from the run's start state and the chunks' last states.
+__global__ void __launch_bounds__(128)
+selective_carry_kernel(SelectiveScanArgs a) {
+    gl_grid_launch_dependents();
+    gl_grid_wait();
+    const int b = blockIdx.y;
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (long long)a.C * a.N) return;
+    const int c = (int)(i / a.N);
+    const int chunks = (a.seq_qlen[b] + a.chunk_len - 1) / a.chunk_len;
+    float S = a.state[(size_t)a.seq_slot[b] * a.state_stride + i];
+    const float A = -expf(a.a_log[i]);
+    for (int k = 0; k < chunks; ++k) {
+        float* slot = a.chunk_state + ((size_t)b * a.n_chunks + k) * a.C * a.N + i;
+        const float last = *slot;
+        *slot = S;
+        S = fmaf(expf(A * a.chunk_dt[((size_t)b * a.n_chunks + k) * a.C + c]), S, last);
     }
 }
 
@@ -535,8 +573,17 @@ static int launch_selective_scan(const SelectiveScanArgs& a, cudaStream_t stream
     const int CPB = RC_THREADS / G;
     const size_t smem = (size_t)SS_CHUNK * (2 * a.N + 3 * CPB) * sizeof(float);
     if (smem > 48 * 1024) return GL_ERR_SMEM;
-    const dim3 grid((a.C + CPB - 1) / CPB, a.B);
-    return gl_launch_in_order(selective_scan_kernel<TA, NPT>, grid, dim3(RC_THREADS), smem, stream, a, G);
+    if (a.n_chunks <= 1) {
+        const dim3 grid((a.C + CPB - 1) / CPB, a.B);
+        return gl_launch_in_order(selective_scan_kernel<TA, NPT, 0>, grid, dim3(RC_THREADS), smem, stream, a, G);
+    }
+    const dim3 grid((a.C + CPB - 1) / CPB, a.B, a.n_chunks);
+    int rc = gl_launch_in_order(selective_scan_kernel<TA, NPT, 1>, grid, dim3(RC_THREADS), smem, stream, a, G);
+    if (rc != 0) return rc;
+    const long long n = (long long)a.C * a.N;
+    rc = gl_launch(selective_carry_kernel, dim3((unsigned)((n + 127) / 128), a.B), dim3(128), 0, stream, 1, a);
+    if (rc != 0) return rc;
+    return gl_launch_in_order(selective_scan_kernel<TA, NPT, 2>, grid, dim3(RC_THREADS), smem, stream, a, G);
 }
 
 static int selective_scan_blocks(const SelectiveScanArgs& a, int npt) {
@@ -544,7 +591,7 @@ static int selective_scan_blocks(const SelectiveScanArgs& a, int npt) {
     while (G * npt < a.N) G <<= 1;
     if (G > 32) return -1;
     const int CPB = RC_THREADS / G;
-    return ((a.C + CPB - 1) / CPB) * a.B;
+    return ((a.C + CPB - 1) / CPB) * a.B * (a.n_chunks > 1 ? a.n_chunks : 1);
 }
 
 template <typename TA>
@@ -567,6 +614,7 @@ GL_API int gl_selective_scan(const SelectiveScanArgs* args, int act_dtype, cudaS
     const SelectiveScanArgs& a = *args;
     if (a.B <= 0) return GL_OK;
     if (a.C <= 0 || a.N <= 0 || a.N > 256 || a.B > 65535) return GL_ERR_SHAPE;
+    if (a.n_chunks > 1 && (!a.chunk_state || !a.chunk_dt || a.chunk_len <= 0 || a.n_chunks > 65535)) return GL_ERR_SHAPE;
     if (act_dtype == GL_F32) return dispatch_selective_scan<float>(a, stream);
     if (act_dtype == GL_BF16) return dispatch_selective_scan<__nv_bfloat16>(a, stream);
     return GL_ERR_DTYPE;

@@ -1022,10 +1022,15 @@ class _SelectiveScanArgs(Structure):
     _fields_ = [("x", c_void_p), ("dtp", c_void_p), ("bc", c_void_p), ("z", c_void_p), ("out", c_void_p),
                 ("a_log", c_void_p), ("d_skip", c_void_p), ("state", c_void_p),
                 ("seq_slot", c_void_p), ("seq_qstart", c_void_p), ("seq_qlen", c_void_p),
-                ("B", c_int), ("C", c_int), ("N", c_int), ("z_ld", c_int), ("z_off", c_int), ("state_stride", c_int)]
+                ("B", c_int), ("C", c_int), ("N", c_int), ("z_ld", c_int), ("z_off", c_int), ("state_stride", c_int),
+                ("chunk_state", c_void_p), ("chunk_dt", c_void_p), ("chunk_len", c_int), ("n_chunks", c_int)]
 
 
 SCAN_MAX_STATE = 256
+# A run of at least SCAN_CHUNKED_FROM tokens is walked as chunks of SCAN_CHUNK_TOKENS side by side (two walks
+# and a carry between them): a token-by-token walk leaves most of the machine idle when the sequences are few.
+SCAN_CHUNK_TOKENS = 256
+SCAN_CHUNKED_FROM = 512
 
 
 def selective_scan(x: torch.Tensor, dtp: torch.Tensor, bc: torch.Tensor, z: torch.Tensor, z_off: int,
@@ -1048,9 +1053,16 @@ def selective_scan(x: torch.Tensor, dtp: torch.Tensor, bc: torch.Tensor, z: torc
     a = _SelectiveScanArgs(x.data_ptr(), dtp.data_ptr(), bc.data_ptr(), z.data_ptr(), out.data_ptr(),
                            a_log.data_ptr(), d_skip.data_ptr(), state.data_ptr(),
                            ctx.seq_slot.data_ptr(), ctx.seq_qstart.data_ptr(), ctx.seq_qlen.data_ptr(),
-                           ctx.n_seqs, C, N, z.shape[1], z_off, state.shape[1])
+                           ctx.n_seqs, C, N, z.shape[1], z_off, state.shape[1], None, None, 0, 0)
+    kernels = 1
+    if ctx.max_qlen >= SCAN_CHUNKED_FROM:
+        chunks = -(-ctx.max_qlen // SCAN_CHUNK_TOKENS)
+        chunk_state = empty((ctx.n_seqs, chunks, C, N), torch.float32, x.device)
+        chunk_dt = empty((ctx.n_seqs, chunks, C), torch.float32, x.device)
+        a.chunk_state, a.chunk_dt = chunk_state.data_ptr(), chunk_dt.data_ptr()
+        a.chunk_len, a.n_chunks, kernels = SCAN_CHUNK_TOKENS, chunks, 3
     fn = _lib("recurrent.cu").gl_selective_scan
-    _check(_launch(fn, byref(a), c_int(dtype_code(x.dtype)), _stream()), "selective_scan")
+    _check(_launch(fn, byref(a), c_int(dtype_code(x.dtype)), _stream()), "selective_scan", kernels)
     return out
 
 

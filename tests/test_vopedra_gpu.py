@@ -216,6 +216,33 @@ def test_long_decoding(dtype):
     m.close()
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_runs_walked_as_chunks(dtype, monkeypatch):
+    """Long runs of the scans are cut into chunks that are walked side by side, with a carry between two
+    walks.  With chunks of 16 tokens from 32 tokens on: a whole prompt (a ragged last chunk), pieces above
+    and below the threshold, and a batch whose shorter sequence has fewer chunks than the longer one."""
+    from gopherllm_b200 import ops
+    monkeypatch.setattr(ops, "SCAN_CHUNK_TOKENS", 16)
+    monkeypatch.setattr(ops, "SCAN_CHUNKED_FROM", 32)
+    for cfg_name in ("ALPHA", "BETA"):
+        cfg = getattr(vm, cfg_name)
+        folder = folder_for(cfg_name, cfg, 5, long_memory=True)
+        toks = tokens_for(cfg, 150, 2)
+        ref = plain_logits(folder, toks)
+        m = load(folder, dtype)
+        for cuts in ([150], [33, 31, 64, 17]):
+            s = m.open_sequence()
+            check(feed(m, s, toks, cuts), ref, dtype, f"{cfg_name} cuts {cuts}")
+            m.close_sequence(s)
+        short = tokens_for(cfg, 37, 3)
+        sa, sb = m.open_sequence(), m.open_sequence()
+        out = m.step([(sa, short), (sb, toks[:100])], [list(range(37)), list(range(100))]).cpu().numpy()
+        check(out[:37], plain_logits(folder, short), dtype, "the shorter of two")
+        check(out[37:], ref[:100], dtype, "the longer of two")
+        m.engine.check_device()
+        m.close()
+
+
 def test_greedy_generation_through_the_scheduler():
     """Model.generate, greedy, for prompts of different lengths in one call: the tokens the plain
     implementation chooses."""
