@@ -619,3 +619,273 @@ GL_API int gl_selective_scan(const SelectiveScanArgs* args, int act_dtype, cudaS
     if (act_dtype == GL_BF16) return dispatch_selective_scan<__nv_bfloat16>(a, stream);
     return GL_ERR_DTYPE;
 }
+
+// ---------------------------------------------------------------------------
+// The matrix memories for long runs: chunks of tokens side by side, a lane a column.
+//
+// Written with a decay a_t[d] and an input b_t[d] per row (gated kind: a = keep_t for every row, b = take_t
+// k_t[d]; bounded forget: a = f_t[d], b = 1 - f_t[d]) a memory is S' = diag(a) S + b v^T, column by column.
+// A thread owns one column and keeps all of its rows in registers: a token costs it two multiply-adds a row
+// and nothing is exchanged between lanes.  The gated kind's normaliser n is one more column whose value is
+// always 1 (its "output" is n.q), so it needs no code of its own.  That mapping has only heads x columns / 32
+// warps of work, so a run is cut into chunks that are walked side by side, twice:
+//   walk 1: every chunk from a zero state; its last state goes to chunk_state;
+//   carry:  S_start[k+1] = diag(P_k) S_start[k] + last_k, P_k[d] the product of the chunk's decays;
+//   walk 2: every chunk from its start, with the raw outputs S^T q (the gated kind's division by
+//           max(|n.q|, e^-m) + 1e-6 follows as a pass of its own over all tokens at once).
+// The gated kind's gates come from a pass of their own: the log gates of all tokens side by side, then the
+// running maximum token by token (a thread a head), which leaves keep, take and e^-m per token.
+// ---------------------------------------------------------------------------
+struct MemoryChunkArgs {
+    const void* proj;         // [T, ld] activation type
+    float* out;               // [T, H*V] raw S^T q
+    float* nq;                // gated: [T, H] n.q
+    float* gates;             // gated: [T, H, 4]: log input gate, log forget gate -> keep, take, e^-m, unused
+    float* state;             // [slots, state_stride]: S [H, D, V], gated: n [H, D], m [H]
+    const float* lower;       // bounded forget: [H*D]
+    float* chunk_state;       // [B, n_chunks, H, D, cols]
+    float* chunk_decay;       // [B, n_chunks, H, D]
+    const int* tok_seq;       // [T]
+    const int* seq_slot;
+    const int* seq_qstart;
+    const int* seq_qlen;
+    int T, ld, q_off, k_off, v_off, i_off, f_off;
+    int B, H, D, V, cols, state_stride, kind, chunk_len, n_chunks;
+    float cap, q_scale;
+};
+
+#define MC_THREADS 128
+#define MC_TOKENS 16
+
+// log gates of every token: gates[t, h, 0] = cap tanh(i / cap), gates[t, h, 1] = logsigmoid(cap tanh(f / cap))
+template <typename TA>
+__global__ void __launch_bounds__(256)
+memory_log_gates_kernel(MemoryChunkArgs a) {
+    gl_grid_launch_dependents();
+    gl_grid_wait();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (long long)a.T * a.H) return;
+    const int t = (int)(i / a.H), h = (int)(i - (long long)t * a.H);
+    const TA* row = (const TA*)a.proj + (size_t)t * a.ld;
+    a.gates[i * 4 + 0] = a.cap * tanhf(gl_load(row + a.i_off + h) / a.cap);
+    a.gates[i * 4 + 1] = rc_log_sigmoid(a.cap * tanhf(gl_load(row + a.f_off + h) / a.cap));
+}
+
+// the running maximum, token by token, a warp a (sequence, head): 32 tokens' log gates are fetched at once, the
+// maximum walks them in registers (every lane follows it, lane j keeps token j's), and the lanes then take
+// keep, take and e^-m of their tokens side by side
+__global__ void __launch_bounds__(32)
+memory_gate_walk_kernel(MemoryChunkArgs a) {
+    gl_grid_launch_dependents();
+    gl_grid_wait();
+    const int b = blockIdx.x / a.H, h = blockIdx.x - b * a.H, lane = threadIdx.x;
+    float* m_g = a.state + (size_t)a.seq_slot[b] * a.state_stride + (size_t)a.H * a.D * a.V + (size_t)a.H * a.D + h;
+    float m = *m_g;
+    const int qstart = a.seq_qstart[b], qlen = a.seq_qlen[b];
+    for (int s0 = 0; s0 < qlen; s0 += 32) {
+        const bool ok = s0 + lane < qlen;
+        float* g = a.gates + ((size_t)(qstart + s0 + (ok ? lane : 0)) * a.H + h) * 4;
+        const float gi = ok ? g[0] : -INFINITY, gf = ok ? g[1] : 0.f;      // a token that is not there leaves m as it is
+        float m_old = 0.f, m_mine = 0.f;
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+            const float m_new = fmaxf(__shfl_sync(0xffffffffu, gf, j) + m, __shfl_sync(0xffffffffu, gi, j));
+            if (lane == j) { m_old = m; m_mine = m_new; }
+            m = m_new;
+        }
+        if (ok) {
+            g[0] = rc_decay(gf + m_old - m_mine);
+            g[1] = expf(gi - m_mine);
+            g[2] = expf(-m_mine);
+        }
+    }
+    if (lane == 0) *m_g = m;
+}
+
+// the product of a chunk's decays per row
+template <typename TA, int KIND>
+__global__ void __launch_bounds__(128)
+memory_chunk_decay_kernel(MemoryChunkArgs a) {
+    gl_grid_launch_dependents();
+    gl_grid_wait();
+    const int b = blockIdx.z / a.n_chunks, chunk = blockIdx.z - b * a.n_chunks, h = blockIdx.y;
+    const int d = blockIdx.x * blockDim.x + threadIdx.x;
+    const int qlen = a.seq_qlen[b], qstart = a.seq_qstart[b];
+    const int t0 = chunk * a.chunk_len, t1 = min(qlen, t0 + a.chunk_len);
+    if (d >= a.D || t0 >= qlen) return;
+    float p = 1.0f;
+    const float l = KIND == 1 ? a.lower[h * a.D + d] : 0.f;
+    for (int s = t0; s < t1; ++s) {
+        if (KIND == 0) p *= a.gates[((size_t)(qstart + s) * a.H + h) * 4];
+        else p *= l + (1.0f - l) * rc_sigmoid(gl_load((const TA*)a.proj + (size_t)(qstart + s) * a.ld + a.f_off + h * a.D + d));
+    }
+    a.chunk_decay[(((size_t)b * a.n_chunks + chunk) * a.H + h) * a.D + d] = p;
+}
+
+// MODE 1: from zero, keep the last state.  MODE 2: from the chunk's start, with outputs.
+template <typename TA, int DMAX, int KIND, int MODE>
+__global__ void __launch_bounds__(MC_THREADS)
+memory_chunk_walk_kernel(MemoryChunkArgs a) {
+    extern __shared__ __align__(16) float smem[];
+    gl_grid_wait();
+    const int D = a.D, V = a.V, H = a.H, cols = a.cols;
+    const int b = blockIdx.z / a.n_chunks, chunk = blockIdx.z - b * a.n_chunks, h = blockIdx.y;
+    const int col0 = blockIdx.x * MC_THREADS, col = col0 + threadIdx.x;
+    const bool live = col < cols;
+    const int qlen = a.seq_qlen[b], qstart = a.seq_qstart[b];
+    const int t0 = chunk * a.chunk_len, t1 = min(qlen, t0 + a.chunk_len);
+    if (t0 >= qlen) return;
+    float* as = smem;                                 // [TOKENS][D] decay (bounded forget; the gated kind's is a scalar)
+    float* bs = as + MC_TOKENS * D;                   // [TOKENS][D] input per row
+    float* qs = bs + MC_TOKENS * D;                   // [TOKENS][D]
+    float* vs = qs + MC_TOKENS * D;                   // [TOKENS][MC_THREADS]
+    float* ks = vs + MC_TOKENS * MC_THREADS;          // [TOKENS] the gated kind's keep
+    float* cs = a.chunk_state + ((((size_t)b * a.n_chunks + chunk) * H + h) * D) * cols;
+    float S[DMAX];
+#pragma unroll
+    for (int d = 0; d < DMAX; ++d) S[d] = (MODE == 2 && live && d < D) ? cs[(size_t)d * cols + col] : 0.f;
+    for (int s0 = t0; s0 < t1; s0 += MC_TOKENS) {
+        const int ns = min(MC_TOKENS, t1 - s0);
+        __syncthreads();
+#pragma unroll 4
+        for (int e = threadIdx.x; e < ns * D; e += MC_THREADS) {
+            const int s = e / D, d = e - s * D;
+            const size_t t = (size_t)(qstart + s0 + s);
+            const TA* row = (const TA*)a.proj + t * a.ld;
+            if (KIND == 0) {
+                bs[e] = a.gates[(t * H + h) * 4 + 1] * gl_load(row + a.k_off + h * D + d);
+                if (MODE == 2) qs[e] = gl_load(row + a.q_off + h * D + d) * a.q_scale;
+            } else {
+                const float l = a.lower[h * D + d];
+                const float f = l + (1.0f - l) * rc_sigmoid(gl_load(row + a.f_off + h * D + d));
+                as[e] = f;
+                bs[e] = 1.0f - f;
+                if (MODE == 2) qs[e] = rc_silu(gl_load(row + a.q_off + h * D + d));
+            }
+        }
+        for (int e = threadIdx.x; e < ns * MC_THREADS; e += MC_THREADS) {
+            const int s = e / MC_THREADS, j = col0 + (e - s * MC_THREADS);
+            const TA* row = (const TA*)a.proj + (size_t)(qstart + s0 + s) * a.ld;
+            vs[e] = j < V ? gl_load(row + a.v_off + h * V + j) : 1.0f;     // the normaliser's column takes 1
+        }
+        if (KIND == 0 && threadIdx.x < ns) ks[threadIdx.x] = a.gates[((size_t)(qstart + s0 + threadIdx.x) * H + h) * 4];
+        __syncthreads();
+        for (int s = 0; s < ns; ++s) {
+            const float v = vs[s * MC_THREADS + threadIdx.x];
+            const float keep = KIND == 0 ? ks[s] : 0.f;
+            const float* ar = as + s * D;
+            const float* br = bs + s * D;
+            const float* qr = qs + s * D;
+            float num = 0.f;
+#pragma unroll
+            for (int d = 0; d < DMAX; ++d) {
+                if (d < D) {
+                    S[d] = fmaf(KIND == 0 ? keep : ar[d], S[d], br[d] * v);
+                    if (MODE == 2) num = fmaf(S[d], qr[d], num);
+                }
+            }
+            if (MODE == 2 && live) {
+                const size_t t = (size_t)(qstart + s0 + s);
+                if (col < V) a.out[t * H * V + (size_t)h * V + col] = num;
+                else a.nq[t * H + h] = num;
+            }
+        }
+    }
+    if (!live) return;
+    if (MODE == 1) {
+#pragma unroll
+        for (int d = 0; d < DMAX; ++d)
+            if (d < D) cs[(size_t)d * cols + col] = S[d];
+    } else if (t1 == qlen) {                          // the run's last chunk: the state row takes its last state
+        float* srow = a.state + (size_t)a.seq_slot[b] * a.state_stride;
+#pragma unroll
+        for (int d = 0; d < DMAX; ++d) {
+            if (d < D) {
+                if (col < V) srow[((size_t)h * D + d) * V + col] = S[d];
+                else srow[(size_t)H * D * V + (size_t)h * D + d] = S[d];
+            }
+        }
+    }
+}
+
+// every chunk's start state from the run's start state and the chunks' last states
+__global__ void __launch_bounds__(128)
+memory_chunk_carry_kernel(MemoryChunkArgs a) {
+    gl_grid_launch_dependents();
+    gl_grid_wait();
+    const int b = blockIdx.z, h = blockIdx.y;
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;        // (row, column)
+    if (i >= a.D * a.cols) return;
+    const int d = i / a.cols, col = i - d * a.cols;
+    const float* srow = a.state + (size_t)a.seq_slot[b] * a.state_stride;
+    float S = col < a.V ? srow[((size_t)h * a.D + d) * a.V + col] : srow[(size_t)a.H * a.D * a.V + (size_t)h * a.D + d];
+    const int chunks = (a.seq_qlen[b] + a.chunk_len - 1) / a.chunk_len;
+    for (int k = 0; k < chunks; ++k) {
+        const size_t at = ((size_t)b * a.n_chunks + k) * a.H + h;
+        float* slot = a.chunk_state + (at * a.D + d) * a.cols + col;
+        const float last = *slot;
+        *slot = S;
+        S = fmaf(a.chunk_decay[at * a.D + d], S, last);
+    }
+}
+
+// the gated kind's outputs divided by max(|n.q|, e^-m) + 1e-6, all tokens at once
+__global__ void __launch_bounds__(256)
+memory_divide_kernel(MemoryChunkArgs a) {
+    gl_grid_launch_dependents();
+    gl_grid_wait();
+    const long long n = (long long)a.T * a.H * a.V;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+        const long long th = i / a.V;
+        a.out[i] = a.out[i] / (fmaxf(fabsf(a.nq[th]), a.gates[th * 4 + 2]) + 1e-6f);
+    }
+}
+
+template <typename TA, int DMAX, int KIND>
+static int launch_memory_chunks(const MemoryChunkArgs& a, cudaStream_t stream) {
+    const size_t smem = (size_t)MC_TOKENS * (3 * a.D + MC_THREADS + 1) * sizeof(float);
+    if (smem > 48 * 1024) return GL_ERR_SMEM;
+    const dim3 walk((a.cols + MC_THREADS - 1) / MC_THREADS, a.H, a.B * a.n_chunks);
+    int rc;
+    if (KIND == 0) {
+        const long long n = (long long)a.T * a.H;
+        rc = gl_launch(memory_log_gates_kernel<TA>, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, 1, a);
+        if (rc != 0) return rc;
+        rc = gl_launch(memory_gate_walk_kernel, dim3(a.B * a.H), dim3(32), 0, stream, 1, a);
+        if (rc != 0) return rc;
+    }
+    rc = gl_launch(memory_chunk_decay_kernel<TA, KIND>, dim3((a.D + 127) / 128, a.H, a.B * a.n_chunks), dim3(128), 0, stream, 1, a);
+    if (rc != 0) return rc;
+    rc = gl_launch_in_order(memory_chunk_walk_kernel<TA, DMAX, KIND, 1>, walk, dim3(MC_THREADS), smem, stream, a);
+    if (rc != 0) return rc;
+    rc = gl_launch(memory_chunk_carry_kernel, dim3((a.D * a.cols + 127) / 128, a.H, a.B), dim3(128), 0, stream, 1, a);
+    if (rc != 0) return rc;
+    rc = gl_launch_in_order(memory_chunk_walk_kernel<TA, DMAX, KIND, 2>, walk, dim3(MC_THREADS), smem, stream, a);
+    if (rc != 0 || KIND != 0) return rc;
+    const long long n = (long long)a.T * a.H * a.V;
+    const long long want = (n + 255) / 256;
+    return gl_launch(memory_divide_kernel, dim3((unsigned)(want > 16384 ? 16384 : want)), dim3(256), 0, stream, 1, a);
+}
+
+template <typename TA, int KIND>
+static int dispatch_memory_chunks(const MemoryChunkArgs& a, cudaStream_t stream) {
+    if (a.D <= 16) return launch_memory_chunks<TA, 16, KIND>(a, stream);
+    if (a.D <= 32) return launch_memory_chunks<TA, 32, KIND>(a, stream);
+    if (a.D <= 64) return launch_memory_chunks<TA, 64, KIND>(a, stream);
+    if (a.D <= 128) return launch_memory_chunks<TA, 128, KIND>(a, stream);
+    return GL_ERR_SHAPE;
+}
+
+// (launches 4 kernels for the bounded-forget kind, 7 for the gated one)
+GL_API int gl_memory_chunks(const MemoryChunkArgs* args, int act_dtype, cudaStream_t stream) {
+    const MemoryChunkArgs& a = *args;
+    if (a.B <= 0 || a.T <= 0) return GL_OK;
+    if (a.H <= 0 || a.D <= 0 || a.D > 128 || a.V <= 0 || a.n_chunks <= 0 || a.chunk_len <= 0) return GL_ERR_SHAPE;
+    if ((a.kind != 0 && a.kind != 1) || a.cols != a.V + (a.kind == 0 ? 1 : 0)) return GL_ERR_SHAPE;
+    if ((long long)a.B * a.n_chunks > 65535 || a.H > 65535) return GL_ERR_SHAPE;
+    if (!a.chunk_state || !a.chunk_decay || (a.kind == 0 && (!a.nq || !a.gates || !(a.cap > 0.f)))) return GL_ERR_SHAPE;
+    if (act_dtype == GL_F32) return a.kind == 0 ? dispatch_memory_chunks<float, 0>(a, stream) : dispatch_memory_chunks<float, 1>(a, stream);
+    if (act_dtype == GL_BF16)
+        return a.kind == 0 ? dispatch_memory_chunks<__nv_bfloat16, 0>(a, stream) : dispatch_memory_chunks<__nv_bfloat16, 1>(a, stream);
+    return GL_ERR_DTYPE;
+}

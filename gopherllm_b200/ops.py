@@ -943,6 +943,20 @@ def memory_state_size(kind: int, H: int, D: int, V: int) -> int:
     return H * D * V + (H * (D + 1) if kind == MEMORY_GATED else 0)
 
 
+class _MemoryChunkArgs(Structure):
+    _fields_ = [("proj", c_void_p), ("out", c_void_p), ("nq", c_void_p), ("gates", c_void_p), ("state", c_void_p),
+                ("lower", c_void_p), ("chunk_state", c_void_p), ("chunk_decay", c_void_p),
+                ("tok_seq", c_void_p), ("seq_slot", c_void_p), ("seq_qstart", c_void_p), ("seq_qlen", c_void_p),
+                ("T", c_int), ("ld", c_int), ("q_off", c_int), ("k_off", c_int), ("v_off", c_int), ("i_off", c_int),
+                ("f_off", c_int), ("B", c_int), ("H", c_int), ("D", c_int), ("V", c_int), ("cols", c_int),
+                ("state_stride", c_int), ("kind", c_int), ("chunk_len", c_int), ("n_chunks", c_int),
+                ("cap", c_float), ("q_scale", c_float)]
+
+
+MEMORY_CHUNKS_MAX_ROWS = 128     # rows a head the chunked walk of the matrix memories takes (a column's rows in registers)
+USE_MEMORY_CHUNKS = True
+
+
 def memory_scan(kind: int, proj: torch.Tensor, state: torch.Tensor, ctx, H: int, D: int, V: int,
                 q_off: int, k_off: int, v_off: int, i_off: int, f_off: int,
                 lower: Optional[torch.Tensor] = None, cap: float = 0.0, q_scale: float = 1.0) -> torch.Tensor:
@@ -957,6 +971,23 @@ def memory_scan(kind: int, proj: torch.Tensor, state: torch.Tensor, ctx, H: int,
     if kind == MEMORY_BOUNDED_FORGET:
         _need(lower, "lower", torch.float32, (H * D,))
     out = empty((T, H * V), torch.float32, proj.device)
+    if USE_MEMORY_CHUNKS and ctx.max_qlen >= SCAN_CHUNKED_FROM and D <= MEMORY_CHUNKS_MAX_ROWS:
+        # a long run: chunks of tokens side by side, a lane a column (two walks and a carry between them)
+        gated = kind == MEMORY_GATED
+        chunks = -(-ctx.max_qlen // SCAN_CHUNK_TOKENS)
+        cols = V + (1 if gated else 0)
+        chunk_state = empty((ctx.n_seqs, chunks, H, D, cols), torch.float32, proj.device)
+        chunk_decay = empty((ctx.n_seqs, chunks, H, D), torch.float32, proj.device)
+        nq = empty((T, H), torch.float32, proj.device) if gated else None
+        gates = empty((T, H, 4), torch.float32, proj.device) if gated else None
+        c = _MemoryChunkArgs(proj.data_ptr(), out.data_ptr(), _addr(nq), _addr(gates), state.data_ptr(), _addr(lower),
+                             chunk_state.data_ptr(), chunk_decay.data_ptr(), ctx.tok_seq.data_ptr(),
+                             ctx.seq_slot.data_ptr(), ctx.seq_qstart.data_ptr(), ctx.seq_qlen.data_ptr(),
+                             T, ld, q_off, k_off, v_off, i_off, f_off, ctx.n_seqs, H, D, V, cols, state.shape[1], kind,
+                             SCAN_CHUNK_TOKENS, chunks, cap, q_scale)
+        fn = _lib("recurrent.cu").gl_memory_chunks
+        _check(_launch(fn, byref(c), c_int(dtype_code(proj.dtype)), _stream()), "memory_chunks", 7 if gated else 4)
+        return out
     # the gated kind's new normaliser and maximum, moved into the state rows by a second kernel
     nm = empty((ctx.n_seqs, H, D + 1), torch.float32, proj.device) if kind == MEMORY_GATED else None
     a = _MemoryScanArgs(proj.data_ptr(), out.data_ptr(), state.data_ptr(), _addr(lower),
