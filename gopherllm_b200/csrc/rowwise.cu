@@ -394,27 +394,38 @@ GL_API int gl_enter_pass(float* x, const float* base, const float* table, int T,
 
 // ---------------------------------------------------------------------------
 // A branch's output normalised over the width and added: 
-//   out[t, :] = alpha * a[t, :] / sqrt(mean(a[t, :]^2) + eps) * w + add0[t, :] + add1[t, :] + add2[t, :]
+//   out[t, :] = alpha * a[t, :] / sqrt(mean(a[t, :]^2) + eps) * w [+ the same of a second branch a2, w2]
+//               + add0[t, :] + add1[t, :] + add2[t, :]
 // (32-bit rows; the adds may be absent; out may be one of them).  One block per row.
 // ---------------------------------------------------------------------------
 __global__ void __launch_bounds__(256)
-rms_scale_add_kernel(const float* a, const float* __restrict__ w, const float* add0, const float* add1, const float* add2,
+rms_scale_add_kernel(const float* a, const float* __restrict__ w, const float* a2, const float* __restrict__ w2,
+                     const float* add0, const float* add1, const float* add2,
                      float* out, int R, int D, float eps, float alpha) {
-    __shared__ float red[8];
+    __shared__ float red[16];
     gl_grid_launch_dependents();
     gl_grid_wait();
     const int r = blockIdx.x;
     const float* src = a + (size_t)r * D;
-    float q = 0.f;
-    for (int d = threadIdx.x; d < D; d += blockDim.x) { const float v = src[d]; q += v * v; }
+    const float* src2 = a2 ? a2 + (size_t)r * D : nullptr;
+    float q = 0.f, q2 = 0.f;
+    for (int d = threadIdx.x; d < D; d += blockDim.x) {
+        const float v = src[d];
+        q += v * v;
+        if (src2) { const float u = src2[d]; q2 += u * u; }
+    }
     q = gl_warp_sum(q);
-    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = q;
+    q2 = gl_warp_sum(q2);
+    const int nw = blockDim.x >> 5;
+    if ((threadIdx.x & 31) == 0) { red[threadIdx.x >> 5] = q; red[8 + (threadIdx.x >> 5)] = q2; }
     __syncthreads();
-    float tot = 0.f;
-    for (int i = 0; i < (int)(blockDim.x >> 5); ++i) tot += red[i];      // same order in every thread
+    float tot = 0.f, tot2 = 0.f;
+    for (int i = 0; i < nw; ++i) { tot += red[i]; tot2 += red[8 + i]; }      // same order in every thread
     const float inv = alpha / sqrtf(tot / (float)D + eps);
+    const float inv2 = alpha / sqrtf(tot2 / (float)D + eps);
     for (int d = threadIdx.x; d < D; d += blockDim.x) {
         float y = src[d] * inv * w[d];
+        if (src2) y += src2[d] * inv2 * w2[d];
         const size_t i = (size_t)r * D + d;
         if (add0) y += add0[i];
         if (add1) y += add1[i];
@@ -423,10 +434,62 @@ rms_scale_add_kernel(const float* a, const float* __restrict__ w, const float* a
     }
 }
 
-GL_API int gl_rms_scale_add(const float* a, const float* w, const float* add0, const float* add1, const float* add2,
+// a2, w2: a second branch normalised the same way and added (may be absent)
+GL_API int gl_rms_scale_add(const float* a, const float* w, const float* a2, const float* w2,
+                            const float* add0, const float* add1, const float* add2,
                             float* out, int R, int D, float eps, float alpha, cudaStream_t stream) {
     if (R <= 0) return GL_OK;
-    if (D <= 0) return GL_ERR_SHAPE;
+    if (D <= 0 || (a2 && !w2)) return GL_ERR_SHAPE;
     const int threads = D >= 2048 ? 256 : (D >= 512 ? 128 : 64);
-    return gl_launch(rms_scale_add_kernel, dim3((unsigned)R), dim3(threads), 0, stream, 1, a, w, add0, add1, add2, out, R, D, eps, alpha);
+    return gl_launch(rms_scale_add_kernel, dim3((unsigned)R), dim3(threads), 0, stream, 1, a, w, a2, w2, add0, add1, add2, out, R, D, eps, alpha);
+}
+
+// ---------------------------------------------------------------------------
+// Two RMS norms of the same 32-bit rows (a layer whose branches each have a norm of their own): the row is
+// read and its mean square taken once, out1 = x * inv * g1, out2 = x * inv * g2.  A warp a row for many
+// rows, a block a row for few.
+// ---------------------------------------------------------------------------
+template <typename TO, int WARP_ROWS>
+__global__ void __launch_bounds__(256)
+rms_norm_pair_kernel(const float* x, const float* __restrict__ g1, const float* __restrict__ g2,
+                     TO* __restrict__ out1, TO* __restrict__ out2, int R, int D, float eps) {
+    __shared__ float red[8];
+    gl_grid_launch_dependents();
+    gl_grid_wait();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int r = WARP_ROWS ? blockIdx.x * (blockDim.x >> 5) + warp : blockIdx.x;
+    if (WARP_ROWS && r >= R) return;
+    const float* src = x + (size_t)r * D;
+    const int first = WARP_ROWS ? lane : threadIdx.x, step = WARP_ROWS ? 32 : blockDim.x;
+    float q = 0.f;
+    for (int d = first; d < D; d += step) { const float v = src[d]; q += v * v; }
+    q = gl_warp_sum(q);
+    if (!WARP_ROWS) {
+        if (lane == 0) red[warp] = q;
+        __syncthreads();
+        q = 0.f;
+        for (int i = 0; i < (int)(blockDim.x >> 5); ++i) q += red[i];      // same order in every thread
+    }
+    const float inv = (float)(1.0 / sqrt((double)(q / (float)D + eps)));
+    for (int d = first; d < D; d += step) {
+        const float v = src[d] * inv;
+        gl_store(out1 + (size_t)r * D + d, v * g1[d]);
+        gl_store(out2 + (size_t)r * D + d, v * g2[d]);
+    }
+}
+
+GL_API int gl_rms_norm_pair(const float* x, const float* g1, const float* g2, void* out1, void* out2, int out_dtype,
+                            int R, int D, float eps, cudaStream_t stream) {
+    if (R <= 0) return GL_OK;
+    if (D <= 0) return GL_ERR_SHAPE;
+    if (R >= 64) {
+        const dim3 grid((unsigned)((R + 7) / 8));
+        if (out_dtype == GL_F32) return gl_launch(rms_norm_pair_kernel<float, 1>, grid, dim3(256), 0, stream, 1, x, g1, g2, (float*)out1, (float*)out2, R, D, eps);
+        if (out_dtype == GL_BF16) return gl_launch(rms_norm_pair_kernel<__nv_bfloat16, 1>, grid, dim3(256), 0, stream, 1, x, g1, g2, (__nv_bfloat16*)out1, (__nv_bfloat16*)out2, R, D, eps);
+        return GL_ERR_DTYPE;
+    }
+    const int threads = D >= 2048 ? 256 : (D >= 512 ? 128 : 64);
+    if (out_dtype == GL_F32) return gl_launch(rms_norm_pair_kernel<float, 0>, dim3((unsigned)R), dim3(threads), 0, stream, 1, x, g1, g2, (float*)out1, (float*)out2, R, D, eps);
+    if (out_dtype == GL_BF16) return gl_launch(rms_norm_pair_kernel<__nv_bfloat16, 0>, dim3((unsigned)R), dim3(threads), 0, stream, 1, x, g1, g2, (__nv_bfloat16*)out1, (__nv_bfloat16*)out2, R, D, eps);
+    return GL_ERR_DTYPE;
 }

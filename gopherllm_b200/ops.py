@@ -1239,11 +1239,32 @@ def enter_pass(x: torch.Tensor, base: Optional[torch.Tensor], table: Optional[to
     return x
 
 
-def rms_scale_add(a: torch.Tensor, w: torch.Tensor, eps: float, alpha: float, adds=(), out: Optional[torch.Tensor] = None):
-    """out = alpha * a / sqrt(mean(a^2) + eps) * w + sum(adds), float32 rows; up to three adds."""
+def rms_norm_pair(x: torch.Tensor, g1: torch.Tensor, g2: torch.Tensor, eps: float, out_dtype: torch.dtype):
+    """Two RMS norms of the same float32 rows with weights g1 and g2, the rows read once."""
+    _need(x, "x", torch.float32)
+    R, D = x.shape
+    _need(g1, "g1", torch.float32, (D,))
+    _need(g2, "g2", torch.float32, (D,))
+    o1 = empty((R, D), out_dtype, x.device)
+    o2 = empty((R, D), out_dtype, x.device)
+    fn = _lib("rowwise.cu").gl_rms_norm_pair
+    _check(_launch(fn, _ptr(x), _ptr(g1), _ptr(g2), _ptr(o1), _ptr(o2), c_int(dtype_code(out_dtype)), c_int(R), c_int(D),
+                   c_float(eps), _stream()), "rms_norm_pair")
+    return o1, o2
+
+
+def rms_scale_add(a: torch.Tensor, w: torch.Tensor, eps: float, alpha: float, adds=(), out: Optional[torch.Tensor] = None,
+                  second=None):
+    """out = alpha * a / sqrt(mean(a^2) + eps) * w + sum(adds), float32 rows; up to three adds.  ``second`` =
+    (a2, w2): a second branch normalised and scaled the same way and added in the same pass."""
     _need(a, "a", torch.float32)
     R, D = a.shape
     _need(w, "w", torch.float32, (D,))
+    a2 = w2 = None
+    if second is not None:
+        a2, w2 = second
+        _need(a2, "a2", torch.float32, (R, D))
+        _need(w2, "w2", torch.float32, (D,))
     adds = list(adds)
     if len(adds) > 3:
         raise KernelError("rms_scale_add adds at most three tensors")
@@ -1254,8 +1275,8 @@ def rms_scale_add(a: torch.Tensor, w: torch.Tensor, eps: float, alpha: float, ad
         out = empty((R, D), torch.float32, a.device)
     _need(out, "out", torch.float32, (R, D))
     fn = _lib("rowwise.cu").gl_rms_scale_add
-    _check(_launch(fn, _ptr(a), _ptr(w), _ptr(adds[0]), _ptr(adds[1]), _ptr(adds[2]), _ptr(out), c_int(R), c_int(D),
-                   c_float(eps), c_float(alpha), _stream()), "rms_scale_add")
+    _check(_launch(fn, _ptr(a), _ptr(w), _ptr(a2), _ptr(w2), _ptr(adds[0]), _ptr(adds[1]), _ptr(adds[2]), _ptr(out),
+                   c_int(R), c_int(D), c_float(eps), c_float(alpha), _stream()), "rms_scale_add")
     return out
 
 

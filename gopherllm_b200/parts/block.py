@@ -168,12 +168,19 @@ class TwoNormParallelBlock(AssembledBlock):
             raise ValueError("the second norm comes with the feed-forward: both or neither")
         super().__init__(spec)
 
+    def _norms(self, x, ctx):
+        """Both branches' inputs; two RMS norms with the same eps read the row once."""
+        a = self.norm.fusable() if self.norm.fusable is not None else None
+        b = self.norm2.fusable() if self.norm2.fusable is not None else None
+        if a is not None and b is not None and a[3] and b[3] and a[1] is None and b[1] is None and a[2] == b[2]:
+            return ops.rms_norm_pair(x, a[0], b[0], a[2], ctx.act_dtype)
+        return self.norm.forward(x, ctx.act_dtype), self.norm2.forward(x, ctx.act_dtype)
+
     def forward(self, x, ctx, cache):
-        xn = self.norm.forward(x, ctx.act_dtype)
         if self.ffn is None:
-            self.mixer.forward(xn, ctx, cache, (x,), x)
+            self.mixer.forward(self.norm.forward(x, ctx.act_dtype), ctx, cache, (x,), x)
             return x
-        xn2 = self.norm2.forward(x, ctx.act_dtype)
+        xn, xn2 = self._norms(x, ctx)
         if self.ffn.until_last is not None and self.mixer.until_last is not None:
             # the branches' last products end on the same rows and columns: one product over the joined K
             # where the kernels can, added onto the residual stream in its epilogue

@@ -265,8 +265,8 @@ class NormedPair(Mixer):
         yl = self.left.forward(xn, ctx, cache[0], (), None)
         yr = self.right.forward(xn, ctx, cache[1], (), None)
         add = [a() if callable(a) else a for a in add]
-        part = ops.rms_scale_add(yl, self.w_left, self.eps, self.weight)
-        return ops.rms_scale_add(yr, self.w_right, self.eps, self.weight, adds=[part] + add, out=out)
+        return ops.rms_scale_add(yl, self.w_left, self.eps, self.weight, adds=add, out=out,
+                                 second=(yr, self.w_right))
 
 
 register_mixer("mlstm", MatrixLstm)
