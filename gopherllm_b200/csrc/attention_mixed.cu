@@ -317,13 +317,14 @@ attn_group_decode_kernel(MixedAttnArgs a) {
                 }
             }
             const int kmin = max(0, lo - j0), kmax = min(GL_PAGE, p - j0 + 1);   // written keys inside the window
-            // eight keys' values are asked for before the first is used: one after the other, every key
+            // sixteen keys' values are asked for before the first is used: one after the other, every key
             // would cost a trip to memory
-            for (int k0 = 0; k0 < GL_PAGE; k0 += 8) {
-                if (k0 + 8 <= kmin || k0 >= kmax) continue;
-                float v[8][NACC];
+            constexpr int KB = NACC <= 2 ? 16 : 8;
+            for (int k0 = 0; k0 < GL_PAGE; k0 += KB) {
+                if (k0 + KB <= kmin || k0 >= kmax) continue;
+                float v[KB][NACC];
 #pragma unroll
-                for (int kk = 0; kk < 8; ++kk) {
+                for (int kk = 0; kk < KB; ++kk) {
                     const bool ok = k0 + kk >= kmin && k0 + kk < kmax;
 #pragma unroll
                     for (int i = 0; i < NACC; ++i) {
@@ -332,7 +333,7 @@ attn_group_decode_kernel(MixedAttnArgs a) {
                     }
                 }
 #pragma unroll
-                for (int kk = 0; kk < 8; ++kk) {
+                for (int kk = 0; kk < KB; ++kk) {
 #pragma unroll
                     for (int g = 0; g < GQ; ++g) {
                         if (g < gq) {

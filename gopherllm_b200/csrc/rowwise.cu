@@ -470,7 +470,17 @@ rms_norm_pair_kernel(const float* x, const float* __restrict__ g1, const float* 
         q = 0.f;
         for (int i = 0; i < (int)(blockDim.x >> 5); ++i) q += red[i];      // same order in every thread
     }
-    const float inv = (float)(1.0 / sqrt((double)(q / (float)D + eps)));
+    // one thread of the row takes the reciprocal square root in 64-bit, as the single norm does
+    float inv = 0.f;
+    if (WARP_ROWS) {
+        if (lane == 0) inv = (float)(1.0 / sqrt((double)(q / (float)D + eps)));
+        inv = __shfl_sync(0xffffffffu, inv, 0);
+    } else {
+        __syncthreads();
+        if (threadIdx.x == 0) red[0] = (float)(1.0 / sqrt((double)(q / (float)D + eps)));
+        __syncthreads();
+        inv = red[0];
+    }
     for (int d = first; d < D; d += step) {
         const float v = src[d] * inv;
         gl_store(out1 + (size_t)r * D + d, v * g1[d]);
