@@ -402,6 +402,30 @@ conv_tail_kernel(ConvArgs a) {
     }
 }
 
+// One token a sequence: a thread owns a (sequence, channel), so it may read the tail, write the output and
+// shift the tail in one go.
+template <typename TA>
+__global__ void __launch_bounds__(256)
+conv_silu_step_kernel(ConvArgs a) {
+    gl_grid_launch_dependents();
+    gl_grid_wait();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (long long)a.B * a.C) return;
+    const int b = (int)(i / a.C), c = (int)(i - (long long)b * a.C);
+    const int back = a.taps - 1, t = a.seq_qstart[b];
+    float* tail = a.state + (size_t)a.seq_slot[b] * a.state_stride + a.tail_off + (size_t)c * back;
+    const float x = gl_load((const TA*)a.x + (size_t)t * a.ld + a.x_off + c);
+    float acc = a.bias[c];
+    for (int j = 0; j < back; ++j) {
+        const float v = tail[j];
+        acc = fmaf(a.w[(size_t)c * a.taps + j], v, acc);
+        if (j > 0) tail[j - 1] = v;                   // (read before the place below it is written)
+    }
+    acc = fmaf(a.w[(size_t)c * a.taps + back], x, acc);
+    if (back > 0) tail[back - 1] = x;
+    gl_store((TA*)a.out + (size_t)t * a.C + c, rc_silu(acc));
+}
+
 GL_API int gl_conv_silu(const ConvArgs* args, int act_dtype, cudaStream_t stream) {
     const ConvArgs& a = *args;
     if (a.T <= 0 || a.B <= 0) return GL_OK;
@@ -409,6 +433,11 @@ GL_API int gl_conv_silu(const ConvArgs* args, int act_dtype, cudaStream_t stream
     const long long n = (long long)a.T * a.C, nb = (long long)a.B * a.C;
     const dim3 g1((unsigned)((n + 255) / 256)), g2((unsigned)((nb + 255) / 256));
     int rc;
+    if (a.T == a.B) {                                 // every sequence brings exactly one token
+        if (act_dtype == GL_F32) return gl_launch(conv_silu_step_kernel<float>, g2, dim3(256), 0, stream, 1, a);
+        if (act_dtype == GL_BF16) return gl_launch(conv_silu_step_kernel<__nv_bfloat16>, g2, dim3(256), 0, stream, 1, a);
+        return GL_ERR_DTYPE;
+    }
     if (act_dtype == GL_F32) {
         rc = gl_launch(conv_silu_kernel<float>, g1, dim3(256), 0, stream, 1, a);
         if (rc == 0 && a.taps > 1) rc = gl_launch(conv_tail_kernel<float>, g2, dim3(256), 0, stream, 1, a);

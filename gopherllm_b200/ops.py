@@ -1045,7 +1045,8 @@ def conv_silu(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor, state: torch
                   ctx.tok_seq.data_ptr(), ctx.seq_slot.data_ptr(), ctx.seq_qstart.data_ptr(), ctx.seq_qlen.data_ptr(),
                   T, ctx.n_seqs, C, taps, ld, x_off, state.shape[1], tail_off)
     fn = _lib("recurrent.cu").gl_conv_silu
-    _check(_launch(fn, byref(a), c_int(dtype_code(x.dtype)), _stream()), "conv_silu", 2 if taps > 1 else 1)
+    _check(_launch(fn, byref(a), c_int(dtype_code(x.dtype)), _stream()), "conv_silu",
+           2 if taps > 1 and T != ctx.n_seqs else 1)
     return out
 
 
