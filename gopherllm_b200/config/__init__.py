@@ -6,12 +6,14 @@ import os
 
 from .registry import (Architecture, architecture_from_config, known_architectures,
                        register_architecture, resolve_architecture)
-from .specs import (BlockSpec, FeedForwardSpec, MixerSpec, ModelSpec, NormSpec, PassEntry,
+from .specs import (BlockSpec, FeedForwardSpec, HashedPairSpec, MixerSpec, ModelSpec, NormSpec, PassEntry,
                     PositionSpec, ScheduleEntry, default_schedule, looped_schedule)
 from . import phi as _phi  # registers the architecture
 from .phi import PhiConfig
 from . import vopedra as _vopedra  # registers the architecture
 from .vopedra import VopedraConfig
+from . import gozolix as _gozolix  # registers the architecture
+from .gozolix import GozolixConfig
 
 
 def read_config_json(folder: str) -> dict:

@@ -104,6 +104,16 @@ class BlockSpec:
 
 
 @dataclass(frozen=True)
+class HashedPairSpec:
+    """A second embedding added to a token's own: row (token before * mul_prev + token * mul_cur) mod
+    ``buckets`` of a table of buckets + 1 rows, whose last row serves a sequence's first token.  The token
+    before a step's first token is kept per sequence, with the cache."""
+    buckets: int
+    mul_prev: int
+    mul_cur: int
+
+
+@dataclass(frozen=True)
 class PassEntry:
     """What happens to the residual stream right before a run that opens a pass over a looped range of
     layers: the stream as it left the embedding is added (``add_embedding``), then row ``index`` of the
@@ -146,6 +156,8 @@ class ModelSpec:
     embedding_norm: Optional[NormSpec] = None
     # rows of the table of learned vectors added at the start of each pass over a looped range; 0: none
     pass_vectors: int = 0
+    # an embedding of the pair (token before, token) added to the token's own; None: none
+    pair_embedding: Optional[HashedPairSpec] = None
 
     def __post_init__(self):
         if self.position_table and self.position_table < self.max_positions:
@@ -175,6 +187,12 @@ class ModelSpec:
     def num_cache_entries(self) -> int:
         ids = [e.cache for e in self.schedule if e.cache is not None]
         return (max(ids) + 1) if ids else 0
+
+    @property
+    def embedding_cache_entry(self) -> Optional[int]:
+        """The cache entry that holds what the embedding keeps per sequence (the token before), behind the
+        entries of the schedule; None if the embedding keeps nothing."""
+        return self.num_cache_entries if self.pair_embedding is not None else None
 
 
 def default_schedule(num_layers: int) -> Tuple[ScheduleEntry, ...]:

@@ -9,6 +9,10 @@
 // sum (a pair's scores come from the query head's own key head), the second mixes.  Without a table
 // the pairs are (g, c(g)) alone and the second kernel only converts.  A query at position p sees keys
 // lo..p, lo = 0 or p-window+1.
+//
+// A score may be shaped before the softmax: s = (q . k) * score_scale; with softcap > 0,
+// s <- softcap * tanh(s / softcap); with a slope per query head, s <- s - slope_h * (p - j) for the
+// key at position j (a penalty that grows with the distance).
 #include "common.cuh"
 
 struct MixedAttnArgs {
@@ -28,7 +32,17 @@ struct MixedAttnArgs {
     float* parts;             // [B, nH, nVal, splits, vd] sums not yet divided
     float* ml;                // [B, nH, splits, 2] each range's maximum and sum
     int splits, pages_per_split;
+    float score_scale;        // multiplies q . k
+    float softcap;            // > 0: scores are capped smoothly at +-softcap
+    const float* slopes;      // [nH] or null: head h's penalty per position of distance
 };
+
+// the shaped score of query head h at position p and the key at position j
+__device__ __forceinline__ float am_shape(float dot, const MixedAttnArgs& a, float slope, int p, int j) {
+    float s = dot * a.score_scale;
+    if (a.softcap > 0.f) s = a.softcap * tanhf(s / a.softcap);
+    return s - slope * (float)(p - j);
+}
 
 #define AM_ROWS 8
 
@@ -63,6 +77,7 @@ attn_pairs_kernel(MixedAttnArgs a) {
     const int lo_cta = (a.window > 0 && p_first - a.window + 1 > 0) ? p_first - a.window + 1 : 0;
 
     float* qv = Qs + warp * hd;
+    const float slope = a.slopes ? a.slopes[g] : 0.f;
     if (live) {
         const TA* qsrc = (const TA*)a.q + ((size_t)(a.seq_qstart[b] + idx) * a.nH + g) * hd;
         for (int d = lane; d < hd; d += 32) qv[d] = gl_load(qsrc + d);
@@ -96,7 +111,7 @@ attn_pairs_kernel(MixedAttnArgs a) {
                 const float* kr = Ks + jj * ks;
                 float d0 = 0.f;
                 for (int d = 0; d < hd; ++d) d0 = fmaf(qv[d], kr[d], d0);
-                s = d0;
+                s = am_shape(d0, a, slope, p, j);
             }
             const float m_new = fmaxf(m, gl_warp_max(s));
             if (m_new == -INFINITY) continue;
@@ -151,6 +166,7 @@ attn_pairs_decode_kernel(MixedAttnArgs a) {
     const int lo = (a.window > 0 && p - a.window + 1 > 0) ? p - a.window + 1 : 0;
     const int row = a.seq_qstart[b];
     const TA* qsrc = (const TA*)a.q + ((size_t)row * a.nH + g) * hd;
+    const float slope = a.slopes ? a.slopes[g] : 0.f;
     for (int d = threadIdx.x; d < hd; d += blockDim.x) qv[d] = gl_load(qsrc + d);
     __syncthreads();
     float acc[NACC];
@@ -172,7 +188,7 @@ attn_pairs_decode_kernel(MixedAttnArgs a) {
                 const TC* kr = kp + (size_t)jj * hd;
                 float d0 = 0.f;
                 for (int d = 0; d < hd; ++d) d0 = fmaf(qv[d], gl_load(kr + d), d0);
-                s = d0;
+                s = am_shape(d0, a, slope, p, j);
             }
             const float m_new = fmaxf(m, gl_warp_max(s));
             if (m_new == -INFINITY) continue;
@@ -291,7 +307,9 @@ attn_group_decode_kernel(MixedAttnArgs a) {
         for (int item = threadIdx.x; item < gq * GL_PAGE; item += AM_GTHREADS) {
             const int g = item / GL_PAGE, key = item - g * GL_PAGE;
             const int j = j0 + key;
-            sc[item] = (j >= lo && j <= p) ? am_dot(qv + g * hd, kp + (size_t)key * hd, hd) : -INFINITY;
+            sc[item] = (j >= lo && j <= p)
+                ? am_shape(am_dot(qv + g * hd, kp + (size_t)key * hd, hd), a, a.slopes ? a.slopes[kh * gq + g] : 0.f, p, j)
+                : -INFINITY;
         }
         __syncthreads();
         if (warp < gq) {

@@ -40,6 +40,9 @@ struct PairsArgs {
     const int* seq_ctx;       // [B]
     const int* pages;         // [B, max_pages]
     int B, nH, nKV, nVal, max_pages, window, max_qlen;
+    float score_scale;        // multiplies q . k
+    float softcap;            // > 0: s <- softcap * tanh(s / softcap)
+    const float* slopes;      // [nH] or null: s <- s - slope_h * (query position - key position)
 };
 
 __device__ __forceinline__ unsigned ap_smem(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
@@ -126,6 +129,8 @@ attn_pairs_tc_kernel(PairsArgs a) {
         for (int e = 0; e < 4; ++e) o[i][e] = 0.f;
     float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
     const float LOG2E = 1.4426950408889634f;
+    const float slope = a.slopes ? a.slopes[h] : 0.f;
+    const bool shaped = a.score_scale != 1.0f || a.softcap > 0.f || a.slopes != nullptr;
     const int r_lo = warp * 16 + grp, r_hi = r_lo + 8;        // this thread's two rows inside the tile
     const int pos_lo = p_first + r_lo, pos_hi = p_first + r_hi;
     const int wlo_lo = (a.window > 0 && pos_lo - a.window + 1 > 0) ? pos_lo - a.window + 1 : 0;
@@ -168,6 +173,18 @@ attn_pairs_tc_kernel(PairsArgs a) {
                     ap_ldm4(sK[st] + r * AP_ROW + c * 16, b0, b1, b2, b3);
                     ap_mma(s[j], qf[kk], b0, b1);
                     ap_mma(s[j + 1], qf[kk], b2, b3);
+                }
+            }
+            if (shaped) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int key = j0 + j * 8 + 2 * t + (e & 1);
+                        float x = s[j][e] * a.score_scale;
+                        if (a.softcap > 0.f) x = a.softcap * tanhf(x / a.softcap);
+                        s[j][e] = x - slope * (float)(((e < 2) ? pos_lo : pos_hi) - key);
+                    }
                 }
             }
             // mask: a row at position x sees keys max(0, x-window+1) .. x

@@ -15,7 +15,9 @@
 enum GlDtype { GL_F32 = 0, GL_BF16 = 1 };
 
 // activation applied in an epilogue
-enum GlAct { GL_ACT_NONE = 0, GL_ACT_GELU_TANH = 1, GL_ACT_GELU_ERF = 2, GL_ACT_RELU = 3 };
+enum GlAct { GL_ACT_NONE = 0, GL_ACT_GELU_TANH = 1, GL_ACT_GELU_ERF = 2, GL_ACT_RELU = 3,
+             GL_ACT_RELU_SQ = 4,      // max(x, 0)^2
+             GL_ACT_SILU = 5 };       // x * sigmoid(x)
 
 // error codes
 enum GlError {
@@ -156,6 +158,8 @@ __device__ __forceinline__ float gl_activate_bf16_grade(float x, int act) {
     }
     if (act == GL_ACT_GELU_ERF) return 0.5f * x * (1.0f + erff(x * 0.70710678118654752440f));
     if (act == GL_ACT_RELU) return fmaxf(x, 0.0f);
+    if (act == GL_ACT_RELU_SQ) { const float r = fmaxf(x, 0.0f); return r * r; }
+    if (act == GL_ACT_SILU) return x / (1.0f + __expf(-x));
     return x;
 }
 
@@ -171,6 +175,12 @@ __device__ __forceinline__ float gl_activate(float x, int act) {
             return 0.5f * x * (1.0f + erff(x * 0.70710678118654752440f));
         case GL_ACT_RELU:
             return fmaxf(x, 0.0f);
+        case GL_ACT_RELU_SQ: {
+            const float r = fmaxf(x, 0.0f);
+            return r * r;
+        }
+        case GL_ACT_SILU:
+            return x / (1.0f + (EXACT ? expf(-x) : __expf(-x)));
         default:
             return x;
     }

@@ -220,6 +220,8 @@ __device__ __forceinline__ void dl_finish_rows(const LayerArgs& a, int phase, in
         if (kind == GL_ACT_GELU_TANH) rows([](float w) { return gl_activate_bf16_grade(w, GL_ACT_GELU_TANH); });
         else if (kind == GL_ACT_GELU_ERF) rows([](float w) { return gl_activate_bf16_grade(w, GL_ACT_GELU_ERF); });
         else if (kind == GL_ACT_RELU) rows([](float w) { return fmaxf(w, 0.0f); });
+        else if (kind == GL_ACT_RELU_SQ) rows([](float w) { const float r = fmaxf(w, 0.0f); return r * r; });
+        else if (kind == GL_ACT_SILU) rows([](float w) { return gl_activate_bf16_grade(w, GL_ACT_SILU); });
         else rows([](float w) { return w; });
     } else {
         const int n = tile * DL_ROWS + nl;

@@ -321,6 +321,8 @@ gemm_tcgen05_kernel(GemmArgs g, const __grid_constant__ CUtensorMap map_a, const
                 case GL_ACT_GELU_TANH: store_tile(std::integral_constant<int, GL_ACT_GELU_TANH>{}); break;
                 case GL_ACT_GELU_ERF: store_tile(std::integral_constant<int, GL_ACT_GELU_ERF>{}); break;
                 case GL_ACT_RELU: store_tile(std::integral_constant<int, GL_ACT_RELU>{}); break;
+                case GL_ACT_RELU_SQ: store_tile(std::integral_constant<int, GL_ACT_RELU_SQ>{}); break;
+                case GL_ACT_SILU: store_tile(std::integral_constant<int, GL_ACT_SILU>{}); break;
                 default: store_tile(std::integral_constant<int, GL_ACT_NONE>{}); break;
             }
             tc_fence_before();

@@ -233,6 +233,9 @@ GL_API int gl_qkv_cache(const QkvCacheArgs* args, int act_dtype, int cache_dtype
 // have another size than its keys:
 //   q <- q / sqrt(mean(q^2) + eps) * gq over nH*hd columns, k likewise over nKV*hd; rotation of the
 //   first 2*half dims of every head; q * q_scale to q_out; k and v into the token's cache row.
+// A query temperature that grows with the position may scale q as well:
+//   q * (1 + temp_coef * ln(floor((pos + 1) / temp_every) + 1))        (temp_every > 0)
+// and a mixer that reads the keys and values another one wrote brings queries alone (q_only).
 // One block per token; statistics, rotation and scale in 32-bit.
 // ---------------------------------------------------------------------------
 struct QkvRowNormArgs {
@@ -250,6 +253,8 @@ struct QkvRowNormArgs {
     int T, ld, nH, nKV, hd, vd, half, max_pages, interleaved, write_kv;
     float eps, q_scale;
     int n_pages;
+    float temp_coef, temp_every;   // query temperature (temp_every <= 0: none)
+    int q_only;                    // the rows hold queries alone; nothing is written to the cache
 };
 
 template <typename TA, typename TC>
@@ -260,7 +265,7 @@ qkv_rownorm_cache_kernel(QkvRowNormArgs a) {
     gl_grid_launch_dependents();
     gl_grid_wait();
     const int t = blockIdx.x;
-    const int nq = a.nH * a.hd, nk = a.nKV * a.hd, nv = a.nKV * a.vd;
+    const int nq = a.nH * a.hd, nk = a.q_only ? 0 : a.nKV * a.hd, nv = a.q_only ? 0 : a.nKV * a.vd;
     const TA* row = (const TA*)a.qkv + (size_t)t * a.ld;
     float* v = smem;                                  // q then k, 32-bit
     float sq = 0.f, sk = 0.f;
@@ -295,7 +300,7 @@ qkv_rownorm_cache_kernel(QkvRowNormArgs a) {
     if (a.half > 0 && a.cosv) {
         const float* cs = a.cosv + (size_t)t * a.half;
         const float* sn = a.sinv + (size_t)t * a.half;
-        const int pairs = (a.nH + a.nKV) * a.half;
+        const int pairs = (a.nH + (a.q_only ? 0 : a.nKV)) * a.half;
         for (int e = threadIdx.x; e < pairs; e += blockDim.x) {
             const int head = e / a.half, i = e - head * a.half;
             float* hv = v + (size_t)head * a.hd;
@@ -309,9 +314,12 @@ qkv_rownorm_cache_kernel(QkvRowNormArgs a) {
         __syncthreads();
     }
     TA* qo = (TA*)a.q_out + (size_t)t * nq;
-    for (int i = threadIdx.x; i < nq; i += blockDim.x) gl_store(qo + i, v[i] * a.q_scale);
-    if (!a.write_kv) return;
     const int pos = a.tok_pos[t];
+    float q_mul = a.q_scale;
+    if (a.temp_every > 0.f)
+        q_mul *= 1.0f + a.temp_coef * logf((float)floor((double)(pos + 1) / (double)a.temp_every) + 1.0f);
+    for (int i = threadIdx.x; i < nq; i += blockDim.x) gl_store(qo + i, v[i] * q_mul);
+    if (!a.write_kv || a.q_only) return;
     const int slot = gl_checked(pos / GL_PAGE, a.max_pages, GL_BAD_POSITION);
     const int page = gl_checked(a.pages[(size_t)a.tok_seq[t] * a.max_pages + slot], a.n_pages > 0 ? a.n_pages : 0x7fffffff, GL_BAD_PAGE);
     for (int i = threadIdx.x; i < nk; i += blockDim.x) {

@@ -51,6 +51,10 @@ __device__ __forceinline__ float rc_decay(float x) {
 //       o = S'^T q / (max(|n'.q|, e^(-m')) + 1e-6).     m starts at 0 (a zeroed state row).
 //   kind 1, forget gate with a lower bound: f = l + (1-l) sigmoid(fpre) per row;
 //       S' = diag(f) S + (1-f) v^T;  o = S'^T q,  q = silu(qpre).
+//   kind 2, gated delta rule: q and k (shared by H / KVH heads) brought to unit length, x / sqrt(sum x^2 + 1e-6),
+//       q times q_scale; beta = sigmoid(b), g = e^(-e^(A_log) softplus(a + dt_bias)) per head, from a second
+//       tensor of projections (``gates``: b at column i_off + h, a at f_off + h);
+//       S <- g S;  u = beta (v - S^T k);  S' = S + k u^T;  o = S'^T q.
 // State row: S [H, D, V], then for kind 0 n [H, D] and m [H].  Every block of a head's columns reads n and m
 // when it starts, and blocks of one head may run one after the other, so the new n and m go to a scratch
 // [B, H, D + 1] first and a second kernel moves them into the rows once all blocks are done.
@@ -67,6 +71,11 @@ struct MemoryScanArgs {
     int B, H, D, V, state_stride, kind;
     float cap, q_scale;
     float* nm_next;           // kind 0: [B, H, D + 1] scratch for the new normaliser and maximum
+    // kind 2:
+    const void* gates;        // [T, gates_ld] activation type: the projections behind beta and the decay
+    const float* a_log;       // [H]
+    const float* dt_bias;     // [H]
+    int gates_ld, KVH;        // KVH: heads of q and k (each shared by H / KVH heads of v)
 };
 
 // FULL: D == R * DPT and D a multiple of 4, so a thread's rows are DPT consecutive ones read as float4 and no
@@ -91,6 +100,7 @@ memory_scan_kernel(MemoryScanArgs a, int R, int CH) {
     float* gs = vs + CH * CT;                   // [CHUNK][4]   kind 0: gi, gf, then keep, take; [.][3] reused
     float* es = gs + CH * 4;                    // [CHUNK]      kind 0: e^(-m')
 
+    const int kh = KIND == 2 ? h / (H / a.KVH) : h;   // the head of q and k this head reads
     float* srow = a.state + (size_t)a.seq_slot[b] * a.state_stride;
     float* S_g = srow + (size_t)h * D * V;
     const float* n_g = srow + (size_t)H * D * V + (size_t)h * D;
@@ -111,10 +121,13 @@ memory_scan_kernel(MemoryScanArgs a, int R, int CH) {
         for (int e = threadIdx.x; e < ns * D; e += MS_THREADS) {
             const int s = e / D, d = e - s * D;
             const TA* row = (const TA*)a.proj + (size_t)(qstart + s0 + s) * a.ld;
-            const float qp = gl_load(row + a.q_off + h * D + d);
+            const float qp = gl_load(row + a.q_off + kh * D + d);
             if (KIND == 0) {
                 qs[e] = qp * a.q_scale;
                 ks[e] = gl_load(row + a.k_off + h * D + d);
+            } else if (KIND == 2) {
+                qs[e] = qp;
+                ks[e] = gl_load(row + a.k_off + kh * D + d);
             } else {
                 qs[e] = rc_silu(qp);
                 const float l = a.lower[h * D + d];
@@ -125,6 +138,27 @@ memory_scan_kernel(MemoryScanArgs a, int R, int CH) {
             const int s = e / CT, j = e - s * CT;
             const TA* row = (const TA*)a.proj + (size_t)(qstart + s0 + s) * a.ld;
             vs[e] = col0 + j < V ? gl_load(row + a.v_off + h * V + col0 + j) : 0.f;
+        }
+        if (KIND == 2) {
+            if (threadIdx.x < ns) {
+                const TA* row = (const TA*)a.gates + (size_t)(qstart + s0 + threadIdx.x) * a.gates_ld;
+                gs[threadIdx.x * 4 + 0] = rc_sigmoid(gl_load(row + a.i_off + h));
+                gs[threadIdx.x * 4 + 1] = rc_decay(-expf(a.a_log[h]) * rc_softplus(gl_load(row + a.f_off + h) + a.dt_bias[h]));
+            }
+            __syncthreads();
+            // unit length: a warp a token
+            for (int s = threadIdx.x >> 5; s < ns; s += MS_THREADS / 32) {
+                float sq = 0.f, sk = 0.f;
+                for (int d = threadIdx.x & 31; d < D; d += 32) {
+                    sq = fmaf(qs[s * D + d], qs[s * D + d], sq);
+                    sk = fmaf(ks[s * D + d], ks[s * D + d], sk);
+                }
+                const float fq = a.q_scale / sqrtf(gl_warp_sum(sq) + 1e-6f), fk = 1.0f / sqrtf(gl_warp_sum(sk) + 1e-6f);
+                for (int d = threadIdx.x & 31; d < D; d += 32) {
+                    qs[s * D + d] *= fq;
+                    ks[s * D + d] *= fk;
+                }
+            }
         }
         if (KIND == 0) {
             if (threadIdx.x < ns) {
@@ -172,7 +206,7 @@ memory_scan_kernel(MemoryScanArgs a, int R, int CH) {
                 for (int i = 0; i < DPT; ++i) {
                     const int d = r + R * i;
                     qr[i] = d < D ? q[d] : 0.f;
-                    kr[i] = d < D ? k[d] : (KIND == 0 ? 0.f : 1.f);      // a row that does not exist keeps its zero
+                    kr[i] = d < D ? k[d] : (KIND == 1 ? 1.f : 0.f);      // a row that does not exist keeps its zero
                 }
             }
             if (KIND == 0) {
@@ -184,6 +218,21 @@ memory_scan_kernel(MemoryScanArgs a, int R, int CH) {
                     n[i] = fmaf(keep, n[i], take * kr[i]);
                     num = fmaf(S[i], qr[i], num);
                     nq = fmaf(n[i], qr[i], nq);
+                }
+            } else if (KIND == 2) {
+                const float beta = gs[s * 4 + 0], decay = gs[s * 4 + 1];
+                float kS = 0.f;
+#pragma unroll
+                for (int i = 0; i < DPT; ++i) {
+                    S[i] *= decay;
+                    kS = fmaf(S[i], kr[i], kS);
+                }
+                for (int o = R >> 1; o > 0; o >>= 1) kS += __shfl_xor_sync(0xffffffffu, kS, o);
+                const float u = beta * (v - kS);
+#pragma unroll
+                for (int i = 0; i < DPT; ++i) {
+                    S[i] = fmaf(kr[i], u, S[i]);
+                    num = fmaf(S[i], qr[i], num);
                 }
             } else {
 #pragma unroll
@@ -245,6 +294,10 @@ static int launch_memory_scan(const MemoryScanArgs& a, cudaStream_t stream) {
         if (full) return gl_launch_in_order(memory_scan_kernel<TA, DPT, 0, true>, grid, dim3(MS_THREADS), smem, stream, a, R, CH);
         return gl_launch_in_order(memory_scan_kernel<TA, DPT, 0, false>, grid, dim3(MS_THREADS), smem, stream, a, R, CH);
     }
+    if (a.kind == 2) {
+        if (full) return gl_launch_in_order(memory_scan_kernel<TA, DPT, 2, true>, grid, dim3(MS_THREADS), smem, stream, a, R, CH);
+        return gl_launch_in_order(memory_scan_kernel<TA, DPT, 2, false>, grid, dim3(MS_THREADS), smem, stream, a, R, CH);
+    }
     if (full) return gl_launch_in_order(memory_scan_kernel<TA, DPT, 1, true>, grid, dim3(MS_THREADS), smem, stream, a, R, CH);
     return gl_launch_in_order(memory_scan_kernel<TA, DPT, 1, false>, grid, dim3(MS_THREADS), smem, stream, a, R, CH);
 }
@@ -296,7 +349,8 @@ GL_API int gl_memory_scan(const MemoryScanArgs* args, int act_dtype, cudaStream_
     const MemoryScanArgs& a = *args;
     if (a.B <= 0) return GL_OK;
     if (a.H <= 0 || a.D <= 0 || a.V <= 0 || a.D > 512 || a.B > 65535 || a.H > 65535) return GL_ERR_SHAPE;
-    if (a.kind != 0 && a.kind != 1) return GL_ERR_SHAPE;
+    if (a.kind < 0 || a.kind > 2) return GL_ERR_SHAPE;
+    if (a.kind == 2 && (!a.gates || !a.a_log || !a.dt_bias || a.KVH <= 0 || a.H % a.KVH)) return GL_ERR_SHAPE;
     if (a.kind == 0 && (!(a.cap > 0.f) || !a.nm_next)) return GL_ERR_SHAPE;
     if (a.state_stride < (long long)a.H * a.D * a.V + (a.kind == 0 ? (long long)a.H * (a.D + 1) : 0)) return GL_ERR_SHAPE;
     if (act_dtype == GL_F32) return dispatch_memory_scan<float>(a, stream);
@@ -308,12 +362,13 @@ GL_API int gl_memory_scan(const MemoryScanArgs* args, int act_dtype, cudaStream_
 // Per-head unit norm of a memory's output, a weight and an optional gate:
 //   out[t, h, j] = o[t, h, j] / sqrt(mean_j o[t, h, :]^2 + eps) * w * sigmoid(gate[t, h*V + j])
 // w is [H*V] (w_per_head = 1) or [V] shared by the heads; gate (activation type, row pitch
-// gate_ld, first column gate_off) may be absent.  One warp per (token, head).
+// gate_ld, first column gate_off) may be absent; gate_silu multiplies by silu(gate) instead of the sigmoid.
+// One warp per (token, head).
 // ---------------------------------------------------------------------------
 template <typename TA>
 __global__ void __launch_bounds__(128)
 head_norm_gate_kernel(const float* o, const float* __restrict__ w, const TA* gate, TA* __restrict__ out,
-                      long long items, int H, int V, int w_per_head, int gate_ld, int gate_off, float eps) {
+                      long long items, int H, int V, int w_per_head, int gate_ld, int gate_off, float eps, int gate_silu) {
     gl_grid_launch_dependents();
     gl_grid_wait();
     const int lane = threadIdx.x & 31;
@@ -327,23 +382,27 @@ head_norm_gate_kernel(const float* o, const float* __restrict__ w, const TA* gat
     const float inv = 1.0f / sqrtf(gl_warp_sum(q) / (float)V + eps);
     for (int j = lane; j < V; j += 32) {
         float y = src[j] * inv * w[w_per_head ? h * V + j : j];
-        if (gate) y *= rc_sigmoid(gl_load(gate + (size_t)t * gate_ld + gate_off + h * V + j));
+        if (gate) {
+            const float z = gl_load(gate + (size_t)t * gate_ld + gate_off + h * V + j);
+            y *= gate_silu ? rc_silu(z) : rc_sigmoid(z);
+        }
         gl_store(out + (size_t)item * V + j, y);
     }
 }
 
 GL_API int gl_head_norm_gate(const float* o, const float* w, const void* gate, void* out, int T, int H, int V,
-                             int w_per_head, int gate_ld, int gate_off, float eps, int act_dtype, cudaStream_t stream) {
+                             int w_per_head, int gate_ld, int gate_off, float eps, int act_dtype, int gate_silu,
+                             cudaStream_t stream) {
     if (T <= 0) return GL_OK;
     if (H <= 0 || V <= 0) return GL_ERR_SHAPE;
     const long long items = (long long)T * H;
     const dim3 grid((unsigned)((items + 3) / 4));
     if (act_dtype == GL_F32)
         return gl_launch(head_norm_gate_kernel<float>, grid, dim3(128), 0, stream, 1, o, w, (const float*)gate, (float*)out,
-                         items, H, V, w_per_head, gate_ld, gate_off, eps);
+                         items, H, V, w_per_head, gate_ld, gate_off, eps, gate_silu);
     if (act_dtype == GL_BF16)
         return gl_launch(head_norm_gate_kernel<__nv_bfloat16>, grid, dim3(128), 0, stream, 1, o, w, (const __nv_bfloat16*)gate,
-                         (__nv_bfloat16*)out, items, H, V, w_per_head, gate_ld, gate_off, eps);
+                         (__nv_bfloat16*)out, items, H, V, w_per_head, gate_ld, gate_off, eps, gate_silu);
     return GL_ERR_DTYPE;
 }
 
@@ -356,7 +415,7 @@ struct ConvArgs {
     const void* x;            // [T, ld] activation type; the convolved channels start at column x_off
     void* out;                // [T, C] activation type
     const float* w;           // [C, taps]
-    const float* bias;        // [C]
+    const float* bias;        // [C] or null
     float* state;             // [slots, state_stride]; the tail [C, taps-1] starts at tail_off
     const int* tok_seq;       // [T]
     const int* seq_slot;
@@ -377,7 +436,7 @@ conv_silu_kernel(ConvArgs a) {
     const int idx = t - a.seq_qstart[b];
     const int back = a.taps - 1;
     const float* tail = a.state + (size_t)a.seq_slot[b] * a.state_stride + a.tail_off + (size_t)c * back;
-    float acc = a.bias[c];
+    float acc = a.bias ? a.bias[c] : 0.f;
     for (int j = 0; j < a.taps; ++j) {
         const int rel = idx - back + j;               // place in the run; negative: before it
         const float v = rel >= 0 ? gl_load((const TA*)a.x + (size_t)(t - back + j) * a.ld + a.x_off + c) : tail[rel + back];
@@ -415,7 +474,7 @@ conv_silu_step_kernel(ConvArgs a) {
     const int back = a.taps - 1, t = a.seq_qstart[b];
     float* tail = a.state + (size_t)a.seq_slot[b] * a.state_stride + a.tail_off + (size_t)c * back;
     const float x = gl_load((const TA*)a.x + (size_t)t * a.ld + a.x_off + c);
-    float acc = a.bias[c];
+    float acc = a.bias ? a.bias[c] : 0.f;
     for (int j = 0; j < back; ++j) {
         const float v = tail[j];
         acc = fmaf(a.w[(size_t)c * a.taps + j], v, acc);

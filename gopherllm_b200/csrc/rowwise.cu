@@ -37,6 +37,66 @@ GL_API int gl_embed(const void* table, int table_dtype, const int* tokens, float
 }
 
 // ---------------------------------------------------------------------------
+// Embedding plus a hashed embedding of the pair (token before, token):
+//   out[t, :] = scale * table[tok, :] + pair_table[(prev * mul_prev + tok * mul_cur) mod buckets, :],
+// a sequence's first token (position 0) taking row ``buckets``, the table's last.  The token before a
+// run's first token is the sequence's state: one int32 per slot (``last_token``, row pitch ``stride``),
+// read by the block of the run's first token, which then stores the run's last token there.
+// ---------------------------------------------------------------------------
+struct EmbedPairArgs {
+    const void* table;        // [V, D]
+    const void* pair_table;   // [buckets + 1, D], same element type
+    const int* tokens;        // [T]
+    const int* tok_seq;       // [T]
+    const int* tok_pos;       // [T]
+    const int* seq_slot;      // [B]
+    const int* seq_qstart;    // [B]
+    const int* seq_qlen;      // [B]
+    int* last_token;          // [slots, stride]
+    float* out;               // [T, D]
+    int T, D, V, buckets, stride;
+    long long mul_prev, mul_cur;
+    float scale;
+};
+
+template <typename TW>
+__global__ void embed_pair_kernel(EmbedPairArgs a) {
+    const int t = blockIdx.x;
+    gl_grid_launch_dependents();
+    gl_grid_wait();
+    int tok = gl_checked(a.tokens[t], a.V, GL_BAD_TOKEN);
+    tok = tok < 0 ? 0 : (tok >= a.V ? a.V - 1 : tok);
+    const int b = a.tok_seq[t];
+    const int qstart = a.seq_qstart[b];
+    const bool first = t == qstart;
+    int* state = a.last_token + (size_t)a.seq_slot[b] * a.stride;
+    const int prev = first ? *state : a.tokens[t - 1];
+    long long row = a.buckets;
+    if (a.tok_pos[t] > 0) {
+        row = ((long long)prev * a.mul_prev + (long long)tok * a.mul_cur) % a.buckets;
+        if (row < 0) row += a.buckets;
+    }
+    const TW* e = (const TW*)a.table + (size_t)tok * a.D;
+    const TW* p = (const TW*)a.pair_table + (size_t)row * a.D;
+    float* o = a.out + (size_t)t * a.D;
+    for (int d = threadIdx.x; d < a.D; d += blockDim.x) o[d] = fmaf(gl_load(e + d), a.scale, gl_load(p + d));
+    if (first) {
+        __syncthreads();                              // every thread has read the state
+        if (threadIdx.x == 0) *state = a.tokens[qstart + a.seq_qlen[b] - 1];
+    }
+}
+
+GL_API int gl_embed_pair(const EmbedPairArgs* args, int table_dtype, cudaStream_t stream) {
+    const EmbedPairArgs& a = *args;
+    if (a.T <= 0) return GL_OK;
+    if (a.D <= 0 || a.V <= 0 || a.buckets <= 0 || a.stride <= 0) return GL_ERR_SHAPE;
+    const int threads = a.D >= 1024 ? 256 : 128;
+    if (table_dtype == GL_F32) return gl_launch(embed_pair_kernel<float>, dim3(a.T), dim3(threads), 0, stream, 1, a);
+    if (table_dtype == GL_BF16) return gl_launch(embed_pair_kernel<__nv_bfloat16>, dim3(a.T), dim3(threads), 0, stream, 1, a);
+    return GL_ERR_DTYPE;
+}
+
+// ---------------------------------------------------------------------------
 // A second table added onto the residual stream: out[t, :] += table[index[t], :].  Learned
 // absolute positions are added once, before the first layer (model.go:2648-2651).
 // ---------------------------------------------------------------------------

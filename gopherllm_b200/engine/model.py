@@ -8,7 +8,7 @@ import torch
 
 from .. import ops
 from ..config.specs import ModelSpec
-from ..parts.base import ParamSpec, build_block, build_norm
+from ..parts.base import ParamSpec, StateRequest, build_block, build_norm
 
 
 def _tensor_addresses(part, prefix: str) -> Dict[str, int]:
@@ -47,6 +47,7 @@ class DecoderModel:
         self.pass_vectors: Optional[torch.Tensor] = None       # one learned vector per pass over a looped range
         self._keeps_embedding = any(e.enter is not None and e.enter.add_embedding for e in spec.schedule)
         self.embedding: Optional[torch.Tensor] = None
+        self.pair_embedding: Optional[torch.Tensor] = None     # hashed embedding of (token before, token), if the spec has it
         self.positions: Optional[torch.Tensor] = None          # learned absolute positions, if the spec has them
         self.head_weight: Optional[torch.Tensor] = None
         self.head_bias: Optional[torch.Tensor] = None
@@ -61,6 +62,8 @@ class DecoderModel:
                 p[f"layers/{i}/{k}"] = v
         if s.position_table:
             p["positions"] = ParamSpec((s.position_table, s.hidden))
+        if s.pair_embedding is not None:
+            p["pair_embedding"] = ParamSpec((s.pair_embedding.buckets + 1, s.hidden))
         for k, v in self.final_norm.parameters().items():
             p[f"final_norm/{k}"] = v
         if self.embedding_norm is not None:
@@ -78,6 +81,7 @@ class DecoderModel:
     def load(self, tensors: Dict[str, torch.Tensor]) -> None:
         self.embedding = tensors["embedding"]
         self.positions = tensors["positions"] if self.spec.position_table else None
+        self.pair_embedding = tensors["pair_embedding"] if self.spec.pair_embedding is not None else None
         for i, b in enumerate(self.blocks):
             pre = f"layers/{i}/"
             b.load({k[len(pre):]: v for k, v in tensors.items() if k.startswith(pre)})
@@ -107,6 +111,7 @@ class DecoderModel:
 
     def _all_tensors(self):
         yield self.embedding
+        yield self.pair_embedding
         yield self.positions
         yield self.head_weight
         yield self.head_bias
@@ -124,6 +129,8 @@ class DecoderModel:
     def cache_requests(self) -> List:
         """What each cache entry must hold: the request of the block whose run writes it."""
         reqs: List = [None] * self.spec.num_cache_entries
+        if self.spec.embedding_cache_entry is not None:
+            reqs.append(StateRequest((1,)))          # the token before, as the bits of an int32
         for e in self.spec.schedule:
             if e.cache is not None and e.writes:
                 reqs[e.cache] = self.blocks[e.layer].cache_request()
@@ -138,14 +145,23 @@ class DecoderModel:
     # -- compute ------------------------------------------------------------
     def forward(self, ctx, cache) -> torch.Tensor:
         """Run the step described by ctx; float32 logits [len(ctx.want_rows), vocab]."""
-        x = self.begin(ctx)
+        x = self.begin(ctx, cache)
         self.run(x, ctx, cache, 0, len(self.spec.schedule))
         return self.finish(x, ctx)
 
     # The same step in three pieces, for a caller that captures it as more than one CUDA graph.
-    def begin(self, ctx) -> torch.Tensor:
-        """The residual stream of the step's tokens, float32 [tokens, hidden]."""
-        x = ops.embed(self.embedding, ctx.tokens, self.spec.embedding_scale)
+    def begin(self, ctx, cache=None) -> torch.Tensor:
+        """The residual stream of the step's tokens, float32 [tokens, hidden].  ``cache`` is needed by an
+        embedding that keeps something per sequence."""
+        pair = self.spec.pair_embedding
+        if pair is not None:
+            if cache is None:
+                raise ValueError("this model's embedding keeps the token before per sequence: begin() needs the cache")
+            last = cache.view(self.spec.embedding_cache_entry).rows.view(torch.int32)
+            x = ops.embed_pair(self.embedding, self.pair_embedding, ctx, last, pair.mul_prev, pair.mul_cur,
+                               self.spec.embedding_scale)
+        else:
+            x = ops.embed(self.embedding, ctx.tokens, self.spec.embedding_scale)
         if self.positions is not None:
             ops.add_rows(self.positions, ctx.tok_pos, x)
         if self.embedding_norm is not None:

@@ -326,7 +326,7 @@ class Engine:
             n_first = min(self.graph_first_runs, n_runs)
             g.first = torch.cuda.CUDAGraph()
             with torch.cuda.graph(g.first, pool=self._graph_pool):
-                g.x = self.model.begin(ctx)
+                g.x = self.model.begin(ctx, self.cache)
                 self.model.run(g.x, ctx, self.cache, 0, n_first)
                 if n_first == n_runs:
                     g.logits = self.model.finish(g.x, ctx)

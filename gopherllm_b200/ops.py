@@ -18,7 +18,9 @@ from .csrc import build, catalog
 
 PAGE = 64                      # tokens per cache page (GL_PAGE)
 F32, BF16 = 0, 1
-ACTIVATIONS = {"none": 0, None: 0, "gelu_new": 1, "gelu_pytorch_tanh": 1, "gelu": 2, "relu": 3}
+ACTIVATIONS = {"none": 0, None: 0, "gelu_new": 1, "gelu_pytorch_tanh": 1, "gelu": 2, "relu": 3,
+               "relu2": 4,      # the square of relu
+               "silu": 5}
 SAMPLE_WINDOW = 64             # tokens the repeat penalty looks back on (runtime.go:27)
 SAMPLE_KMAX = 1024
 
@@ -272,6 +274,37 @@ def add_rows(table: torch.Tensor, index: torch.Tensor, out: torch.Tensor) -> tor
     fn = _lib("rowwise.cu").gl_add_rows
     _check(_launch(fn, _ptr(table), c_int(dtype_code(table.dtype)), _ptr(index), _ptr(out),
               c_int(index.numel()), c_int(D), c_int(N), _stream()), "add_rows")
+    return out
+
+
+class _EmbedPairArgs(Structure):
+    _fields_ = [("table", c_void_p), ("pair_table", c_void_p), ("tokens", c_void_p), ("tok_seq", c_void_p),
+                ("tok_pos", c_void_p), ("seq_slot", c_void_p), ("seq_qstart", c_void_p), ("seq_qlen", c_void_p),
+                ("last_token", c_void_p), ("out", c_void_p),
+                ("T", c_int), ("D", c_int), ("V", c_int), ("buckets", c_int), ("stride", c_int),
+                ("mul_prev", ctypes.c_longlong), ("mul_cur", ctypes.c_longlong), ("scale", c_float)]
+
+
+def embed_pair(table: torch.Tensor, pair_table: torch.Tensor, ctx, last_token: torch.Tensor, mul_prev: int,
+               mul_cur: int, scale: float = 1.0) -> torch.Tensor:
+    """out[t] = scale * table[token] + pair_table[(token before * mul_prev + token * mul_cur) mod buckets] as
+    float32, buckets = rows of pair_table - 1; a sequence's first token takes the last row.  ``last_token``
+    [slots, n] int32 holds, in column 0 of a sequence's row, the token before the step's first; it receives the
+    step's last."""
+    _need(table, "table")
+    _need(pair_table, "pair_table", table.dtype)
+    _need(last_token, "last_token", torch.int32)
+    V, D = table.shape
+    if pair_table.shape[1] != D or pair_table.shape[0] < 2 or last_token.dim() != 2:
+        raise KernelError(f"embed_pair: tables {tuple(table.shape)} and {tuple(pair_table.shape)} do not fit")
+    T = ctx.tokens.numel()
+    out = empty((T, D), torch.float32, table.device)
+    a = _EmbedPairArgs(table.data_ptr(), pair_table.data_ptr(), ctx.tokens.data_ptr(), ctx.tok_seq.data_ptr(),
+                       ctx.tok_pos.data_ptr(), ctx.seq_slot.data_ptr(), ctx.seq_qstart.data_ptr(), ctx.seq_qlen.data_ptr(),
+                       last_token.data_ptr(), out.data_ptr(), T, D, V, pair_table.shape[0] - 1, last_token.shape[1],
+                       int(mul_prev), int(mul_cur), scale)
+    fn = _lib("rowwise.cu").gl_embed_pair
+    _check(_launch(fn, byref(a), c_int(dtype_code(table.dtype)), _stream()), "embed_pair")
     return out
 
 
@@ -929,10 +962,11 @@ class _MemoryScanArgs(Structure):
                 ("seq_slot", c_void_p), ("seq_qstart", c_void_p), ("seq_qlen", c_void_p),
                 ("ld", c_int), ("q_off", c_int), ("k_off", c_int), ("v_off", c_int), ("i_off", c_int), ("f_off", c_int),
                 ("B", c_int), ("H", c_int), ("D", c_int), ("V", c_int), ("state_stride", c_int), ("kind", c_int),
-                ("cap", c_float), ("q_scale", c_float), ("nm_next", c_void_p)]
+                ("cap", c_float), ("q_scale", c_float), ("nm_next", c_void_p),
+                ("gates", c_void_p), ("a_log", c_void_p), ("dt_bias", c_void_p), ("gates_ld", c_int), ("KVH", c_int)]
 
 
-MEMORY_GATED, MEMORY_BOUNDED_FORGET = 0, 1
+MEMORY_GATED, MEMORY_BOUNDED_FORGET, MEMORY_DELTA = 0, 1, 2
 
 
 def memory_state_size(kind: int, H: int, D: int, V: int) -> int:
@@ -959,11 +993,21 @@ USE_MEMORY_CHUNKS = True
 
 def memory_scan(kind: int, proj: torch.Tensor, state: torch.Tensor, ctx, H: int, D: int, V: int,
                 q_off: int, k_off: int, v_off: int, i_off: int, f_off: int,
-                lower: Optional[torch.Tensor] = None, cap: float = 0.0, q_scale: float = 1.0) -> torch.Tensor:
+                lower: Optional[torch.Tensor] = None, cap: float = 0.0, q_scale: float = 1.0,
+                gates: Optional[torch.Tensor] = None, a_log: Optional[torch.Tensor] = None,
+                dt_bias: Optional[torch.Tensor] = None, kv_heads: int = 0) -> torch.Tensor:
     """A matrix memory's run over the step's tokens: float32 [T, H*V], each head's S^T q (divided by the
     gated kind's normaliser); ``state`` [slots, size] float32 is read at ctx.seq_slot and written back.
-    ``proj`` [T, ld] holds the projections at the given column offsets."""
+    ``proj`` [T, ld] holds the projections at the given column offsets.  MEMORY_DELTA (the gated delta rule):
+    q and k have ``kv_heads`` heads, each read by H / kv_heads heads; ``gates`` [T, ld'] holds the projection
+    behind beta at column i_off + h and the one behind the decay at f_off + h; ``a_log`` and ``dt_bias`` [H]."""
     _need(proj, "proj")
+    if kind == MEMORY_DELTA:
+        _need(gates, "gates", proj.dtype)
+        _need(a_log, "a_log", torch.float32, (H,))
+        _need(dt_bias, "dt_bias", torch.float32, (H,))
+        if kv_heads <= 0 or H % kv_heads or gates.shape[0] != proj.shape[0]:
+            raise KernelError(f"memory_scan: {H} heads do not share {kv_heads} heads of q and k")
     _need(state, "state", torch.float32)
     T, ld = proj.shape
     if state.shape[1] < memory_state_size(kind, H, D, V):
@@ -971,7 +1015,8 @@ def memory_scan(kind: int, proj: torch.Tensor, state: torch.Tensor, ctx, H: int,
     if kind == MEMORY_BOUNDED_FORGET:
         _need(lower, "lower", torch.float32, (H * D,))
     out = empty((T, H * V), torch.float32, proj.device)
-    if USE_MEMORY_CHUNKS and ctx.max_qlen >= SCAN_CHUNKED_FROM and D <= MEMORY_CHUNKS_MAX_ROWS:
+    if (USE_MEMORY_CHUNKS and kind != MEMORY_DELTA and ctx.max_qlen >= SCAN_CHUNKED_FROM
+            and D <= MEMORY_CHUNKS_MAX_ROWS):
         # a long run: chunks of tokens side by side, a lane a column (two walks and a carry between them)
         gated = kind == MEMORY_GATED
         chunks = -(-ctx.max_qlen // SCAN_CHUNK_TOKENS)
@@ -993,16 +1038,20 @@ def memory_scan(kind: int, proj: torch.Tensor, state: torch.Tensor, ctx, H: int,
     a = _MemoryScanArgs(proj.data_ptr(), out.data_ptr(), state.data_ptr(), _addr(lower),
                         ctx.seq_slot.data_ptr(), ctx.seq_qstart.data_ptr(), ctx.seq_qlen.data_ptr(),
                         ld, q_off, k_off, v_off, i_off, f_off, ctx.n_seqs, H, D, V, state.shape[1], kind, cap, q_scale,
-                        _addr(nm))
+                        _addr(nm), _addr(gates), _addr(a_log), _addr(dt_bias),
+                        gates.shape[1] if gates is not None else 0, kv_heads)
     fn = _lib("recurrent.cu").gl_memory_scan
     _check(_launch(fn, byref(a), c_int(dtype_code(proj.dtype)), _stream()), "memory_scan", 2 if kind == MEMORY_GATED else 1)
     return out
 
 
 def head_norm_gate(o: torch.Tensor, w: torch.Tensor, H: int, V: int, eps: float, out_dtype: torch.dtype,
-                   gate: Optional[torch.Tensor] = None, gate_off: int = 0) -> torch.Tensor:
+                   gate: Optional[torch.Tensor] = None, gate_off: int = 0, gate_act: str = "sigmoid") -> torch.Tensor:
     """Each head of float32 ``o`` [T, H*V] divided by its root mean square, times ``w`` ([H*V], or [V]
-    shared by the heads), times sigmoid of the gate's columns gate_off.. of ``gate`` [T, ld] if given."""
+    shared by the heads), times sigmoid (``gate_act`` "silu": silu) of the gate's columns gate_off.. of
+    ``gate`` [T, ld] if given."""
+    if gate_act not in ("sigmoid", "silu"):
+        raise KernelError(f"head_norm_gate: gate activation {gate_act!r} unknown")
     _need(o, "o", torch.float32)
     T = o.shape[0]
     _need(o, "o", shape=(T, H * V))
@@ -1016,7 +1065,7 @@ def head_norm_gate(o: torch.Tensor, w: torch.Tensor, H: int, V: int, eps: float,
     _check(_launch(fn, _ptr(o), _ptr(w), _ptr(gate), _ptr(out), c_int(T), c_int(H), c_int(V),
                    c_int(0 if w.numel() == V else 1),
                    c_int(0 if gate is None else gate.shape[1]), c_int(gate_off), c_float(eps),
-                   c_int(dtype_code(out_dtype)), _stream()), "head_norm_gate")
+                   c_int(dtype_code(out_dtype)), c_int(1 if gate_act == "silu" else 0), _stream()), "head_norm_gate")
     return out
 
 
@@ -1027,7 +1076,7 @@ class _ConvArgs(Structure):
                 ("state_stride", c_int), ("tail_off", c_int)]
 
 
-def conv_silu(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor, state: torch.Tensor, tail_off: int, ctx,
+def conv_silu(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], state: torch.Tensor, tail_off: int, ctx,
               x_off: int = 0) -> torch.Tensor:
     """silu of a causal per-channel convolution over columns x_off.. of ``x`` [T, ld]; ``w`` [C, taps] with the
     current token's tap last.  The inputs before a run come from ``state`` (the last taps-1 inputs of each
@@ -1035,13 +1084,14 @@ def conv_silu(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor, state: torch
     _need(x, "x")
     _need(w, "w", torch.float32)
     C, taps = w.shape
-    _need(bias, "bias", torch.float32, (C,))
+    if bias is not None:
+        _need(bias, "bias", torch.float32, (C,))
     _need(state, "state", torch.float32)
     T, ld = x.shape
     if x_off + C > ld or tail_off + C * (taps - 1) > state.shape[1]:
         raise KernelError("conv_silu: columns or state row too small")
     out = empty((T, C), x.dtype, x.device)
-    a = _ConvArgs(x.data_ptr(), out.data_ptr(), w.data_ptr(), bias.data_ptr(), state.data_ptr(),
+    a = _ConvArgs(x.data_ptr(), out.data_ptr(), w.data_ptr(), _addr(bias), state.data_ptr(),
                   ctx.tok_seq.data_ptr(), ctx.seq_slot.data_ptr(), ctx.seq_qstart.data_ptr(), ctx.seq_qlen.data_ptr(),
                   T, ctx.n_seqs, C, taps, ld, x_off, state.shape[1], tail_off)
     fn = _lib("recurrent.cu").gl_conv_silu
@@ -1104,20 +1154,29 @@ class _QkvRowNormArgs(Structure):
                 ("tok_seq", c_void_p), ("tok_pos", c_void_p), ("pages", c_void_p),
                 ("T", c_int), ("ld", c_int), ("nH", c_int), ("nKV", c_int), ("hd", c_int), ("vd", c_int),
                 ("half", c_int), ("max_pages", c_int), ("interleaved", c_int), ("write_kv", c_int),
-                ("eps", c_float), ("q_scale", c_float), ("n_pages", c_int)]
+                ("eps", c_float), ("q_scale", c_float), ("n_pages", c_int),
+                ("temp_coef", c_float), ("temp_every", c_float), ("q_only", c_int)]
 
 
 def qkv_rownorm_to_cache(qkv: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, ctx, pages: torch.Tensor,
                          num_heads: int, num_kv_heads: int, head_dim: int, value_dim: int, q_scale: float,
                          cos: Optional[torch.Tensor], sin: Optional[torch.Tensor], interleaved: bool,
                          q_gamma: Optional[torch.Tensor], k_gamma: Optional[torch.Tensor], eps: float,
-                         write_kv: bool = True) -> torch.Tensor:
+                         write_kv: bool = True, q_temp: Optional[tuple] = None, q_only: bool = False) -> torch.Tensor:
     """Queries and keys normalised over the whole projection (root mean square, weights [nH*hd] and
     [nKV*hd]; None: no norm), rotated and scaled; keys and values written to the tokens' cache rows.
-    qkv [T, ld]: q, k, v side by side from column 0.  Returns q [T, nH*hd]."""
+    qkv [T, ld]: q, k, v side by side from column 0 (``q_only``: queries alone, nothing is written).
+    ``q_temp`` = (coef, every): q also times 1 + coef * ln(floor((position + 1) / every) + 1).
+    Returns q [T, nH*hd]."""
     _need(qkv, "qkv")
     T, ld = qkv.shape
     nq, nk, nv = num_heads * head_dim, num_kv_heads * head_dim, num_kv_heads * value_dim
+    if q_only:
+        nk = nv = 0
+        if write_kv:
+            raise KernelError("qkv_rownorm_to_cache: rows of queries alone have nothing to write to the cache")
+    if q_temp is not None and not q_temp[1] > 0:
+        raise KernelError("qkv_rownorm_to_cache: the query temperature's period must be positive")
     if ld < nq + nk + nv:
         raise KernelError("qkv_rownorm_to_cache: the projection's rows are too short")
     if tuple(k_cache.shape[1:]) != (num_kv_heads, PAGE, head_dim) or tuple(v_cache.shape[1:]) != (num_kv_heads, PAGE, value_dim):
@@ -1135,7 +1194,9 @@ def qkv_rownorm_to_cache(qkv: torch.Tensor, k_cache: torch.Tensor, v_cache: torc
     a = _QkvRowNormArgs(qkv.data_ptr(), q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), _addr(cos), _addr(sin),
                         _addr(q_gamma), _addr(k_gamma), ctx.tok_seq.data_ptr(), ctx.tok_pos.data_ptr(), pages.data_ptr(),
                         T, ld, num_heads, num_kv_heads, head_dim, value_dim, half, pages.shape[-1],
-                        1 if interleaved else 0, 1 if write_kv else 0, eps, q_scale, k_cache.shape[0])
+                        1 if interleaved else 0, 1 if write_kv else 0, eps, q_scale, k_cache.shape[0],
+                        q_temp[0] if q_temp is not None else 0.0, q_temp[1] if q_temp is not None else 0.0,
+                        1 if q_only else 0)
     fn = _lib("qkv_cache.cu").gl_qkv_rownorm_cache
     _check(_launch(fn, byref(a), c_int(dtype_code(qkv.dtype)), c_int(dtype_code(k_cache.dtype)), _stream()),
            "qkv_rownorm_to_cache")
@@ -1147,7 +1208,8 @@ class _MixedAttnArgs(Structure):
                 ("mix", c_void_p), ("seq_qstart", c_void_p), ("seq_qlen", c_void_p), ("seq_ctx", c_void_p), ("pages", c_void_p),
                 ("T", c_int), ("B", c_int), ("nH", c_int), ("nKV", c_int), ("hd", c_int), ("vd", c_int),
                 ("max_pages", c_int), ("window", c_int), ("max_qlen", c_int), ("n_pages", c_int),
-                ("parts", c_void_p), ("ml", c_void_p), ("splits", c_int), ("pages_per_split", c_int)]
+                ("parts", c_void_p), ("ml", c_void_p), ("splits", c_int), ("pages_per_split", c_int),
+                ("score_scale", c_float), ("softcap", c_float), ("slopes", c_void_p)]
 
 
 def mixed_decode_splits(batch: int, num_kv_heads: int, max_len: int, device) -> int:
@@ -1162,7 +1224,7 @@ class _PairsArgs(Structure):
     _fields_ = [("q", c_void_p), ("pairs", c_void_p), ("k_cache", c_void_p), ("v_cache", c_void_p),
                 ("seq_qstart", c_void_p), ("seq_qlen", c_void_p), ("seq_ctx", c_void_p), ("pages", c_void_p),
                 ("B", c_int), ("nH", c_int), ("nKV", c_int), ("nVal", c_int), ("max_pages", c_int), ("window", c_int),
-                ("max_qlen", c_int)]
+                ("max_qlen", c_int), ("score_scale", c_float), ("softcap", c_float), ("slopes", c_void_p)]
 
 
 USE_PAIRS_TC = True
@@ -1170,10 +1232,13 @@ USE_PAIRS_TC = True
 
 def attention_mixed(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, ctx, pages: torch.Tensor,
                     num_heads: int, num_kv_heads: int, head_dim: int, value_dim: int,
-                    mix: Optional[torch.Tensor] = None, window: int = 0) -> torch.Tensor:
+                    mix: Optional[torch.Tensor] = None, window: int = 0, score_scale: float = 1.0,
+                    softcap: float = 0.0, slopes: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Causal softmax attention of scaled queries [T, nH*hd] over the paged cache; with ``mix`` [nH, nH]
     head h applies sum_g mix[h, g] * (head g's softmax weights) to the values of its own key/value
-    head.  Returns [T, nH*vd] in q's type.  Prompts in bfloat16 with key and value sizes that are
+    head.  A score is (q . k) * score_scale, then softcap * tanh(score / softcap) when softcap > 0, then
+    minus slopes[h] * (query position - key position) when ``slopes`` [nH] float32 is given.
+    Returns [T, nH*vd] in q's type.  Prompts in bfloat16 with key and value sizes that are
     multiples of 16 compute the (query head, value head) pairs on the tensor cores (a library per pair
     of sizes); everything else runs the 32-bit kernels."""
     _need(q, "q")
@@ -1181,13 +1246,15 @@ def attention_mixed(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
     _need(q, "q", shape=(T, num_heads * head_dim))
     if mix is not None:
         _need(mix, "mix", torch.float32, (num_heads, num_heads))
+    if slopes is not None:
+        _need(slopes, "slopes", torch.float32, (num_heads,))
     n_val = num_kv_heads if mix is not None else 1
     pairs = empty((T, num_heads, n_val, value_dim), torch.float32, q.device)
     out = empty((T, num_heads * value_dim), q.dtype, q.device)
     a = _MixedAttnArgs(q.data_ptr(), pairs.data_ptr(), out.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), _addr(mix),
                        ctx.seq_qstart.data_ptr(), ctx.seq_qlen.data_ptr(), ctx.seq_ctx.data_ptr(), pages.data_ptr(),
                        T, ctx.n_seqs, num_heads, num_kv_heads, head_dim, value_dim, pages.shape[-1], window,
-                       ctx.max_qlen, k_cache.shape[0], None, None, 0, 0)
+                       ctx.max_qlen, k_cache.shape[0], None, None, 0, 0, score_scale, softcap, _addr(slopes))
     if ctx.max_qlen == 1 and num_heads // num_kv_heads <= 8 and num_kv_heads <= 8 and value_dim <= 128:
         # one token a sequence: the context in ranges of pages, a block each (sized for the step's longest
         # sequence; a captured step is sized for its bucket's longest), put together by the mixing kernel
@@ -1202,7 +1269,8 @@ def attention_mixed(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
             and head_dim % 16 == 0 and value_dim % 16 == 0 and not DEBUG_BOUNDS):
         p = _PairsArgs(q.data_ptr(), pairs.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(),
                        ctx.seq_qstart.data_ptr(), ctx.seq_qlen.data_ptr(), ctx.seq_ctx.data_ptr(), pages.data_ptr(),
-                       ctx.n_seqs, num_heads, num_kv_heads, n_val, pages.shape[-1], window, ctx.max_qlen)
+                       ctx.n_seqs, num_heads, num_kv_heads, n_val, pages.shape[-1], window, ctx.max_qlen,
+                       score_scale, softcap, _addr(slopes))
         fn = _lib("attention_mixed_tc.cu", catalog.pair_dim_defines(head_dim, value_dim)).gl_attention_pairs_tc
         _check(_launch(fn, byref(p), _stream()), "attention_pairs_tc")
         _check(_launch(lib.gl_head_mix, byref(a), c_int(dtype_code(q.dtype)), _stream()), "head_mix")
@@ -1222,6 +1290,96 @@ def gated_act(gu: torch.Tensor, act) -> torch.Tensor:
     fn = _lib("rowwise.cu").gl_gated_act
     _check(_launch(fn, _ptr(gu), _ptr(out), c_int(T), c_int(F2 // 2), c_int(ACTIVATIONS[act]),
                    c_int(dtype_code(gu.dtype)), _stream()), "gated_act")
+    return out
+
+
+# ---------------------------------------------------------------------------
+# A mixture of experts (csrc/moe.cu)
+MOE_TILE_ROWS = 32
+
+
+class _RouteArgs(Structure):
+    _fields_ = [("logits", c_void_p), ("ids", c_void_p), ("weights", c_void_p),
+                ("T", c_int), ("E", c_int), ("top", c_int), ("groups", c_int), ("keep", c_int), ("scale", c_float)]
+
+
+def moe_route(logits: torch.Tensor, top: int, groups: int = 1, keep: int = 1, scale: float = 1.0):
+    """Each token's ``top`` experts by sigmoid(logits) and their weights score / (sum of the chosen scores +
+    1e-20) * scale: (ids int32 [T, top], weights float32 [T, top]).  With ``groups`` > 1 the experts form that
+    many equal groups of neighbours; a group's score is the sum of its two largest scores and only experts of
+    the best ``keep`` groups are chosen from."""
+    _need(logits, "logits", torch.float32)
+    T, E = logits.shape
+    if not (0 < top <= E and groups >= 1 and E % groups == 0 and 1 <= keep <= groups and keep * (E // groups) >= top):
+        raise KernelError(f"moe_route: top {top} of {E} experts in {groups} groups of which {keep} stay is not possible")
+    ids = empty((T, top), torch.int32, logits.device)
+    weights = empty((T, top), torch.float32, logits.device)
+    a = _RouteArgs(logits.data_ptr(), ids.data_ptr(), weights.data_ptr(), T, E, top, groups, keep, scale)
+    _check(_launch(_lib("moe.cu").gl_moe_route, byref(a), _stream()), "moe_route")
+    return ids, weights
+
+
+class _PlanArgs(Structure):
+    _fields_ = [("ids", c_void_p), ("order", c_void_p), ("tile_expert", c_void_p), ("tile_start", c_void_p),
+                ("tile_rows", c_void_p), ("n_tiles", c_void_p), ("A", c_int), ("E", c_int), ("max_tiles", c_int)]
+
+
+class _ExpertArgs(Structure):
+    _fields_ = [("x", c_void_p), ("w", c_void_p), ("out", c_void_p), ("order", c_void_p), ("tile_expert", c_void_p),
+                ("tile_start", c_void_p), ("tile_rows", c_void_p), ("n_tiles", c_void_p), ("weights", c_void_p),
+                ("A", c_int), ("N", c_int), ("K", c_int), ("top", c_int), ("max_tiles", c_int)]
+
+
+USE_MOE_TC = True        # bfloat16 experts on the tensor cores (False: the CUDA-core kernels, for comparison)
+
+
+def moe_experts(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, w_gate_up: torch.Tensor,
+                w_down: torch.Tensor, add: Optional[torch.Tensor] = None,
+                out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[t] = sum_k weights[t, k] * down_e(silu(gate_e(x[t])) * up_e(x[t])) + add[t], e = ids[t, k]; float32
+    [T, hidden].  w_gate_up [E, 2F, K] holds every expert's gate rows and then its up rows, w_down [E, hidden, F].
+    The step's (token, choice) pairs are sorted by expert on the device and cut into tiles of rows; the grids
+    cover the most tiles any choice can make, so nothing depends on the host knowing what the router chose."""
+    _need(x, "x")
+    T, K = x.shape
+    _need(ids, "ids", torch.int32)
+    top = ids.shape[1]
+    _need(weights, "weights", torch.float32, (T, top))
+    _need(w_gate_up, "w_gate_up")
+    _need(w_down, "w_down", w_gate_up.dtype)
+    E, F2, Kw = w_gate_up.shape
+    F = F2 // 2
+    hidden = w_down.shape[1]
+    if Kw != K or F2 % 2 or tuple(w_down.shape) != (E, hidden, F) or tuple(ids.shape) != (T, top):
+        raise KernelError(f"moe_experts: weights {tuple(w_gate_up.shape)} / {tuple(w_down.shape)} do not fit x {tuple(x.shape)}")
+    if add is not None:
+        _need(add, "add", torch.float32, (T, hidden))
+    if out is None:
+        out = empty((T, hidden), torch.float32, x.device)
+    _need(out, "out", torch.float32, (T, hidden))
+    A = T * top
+    max_tiles = -(-A // MOE_TILE_ROWS) + min(E, A)
+    dev = x.device
+    # (each a tensor of its own: a tape of launches knows temporaries by their first address)
+    order = empty((A,), torch.int32, dev)
+    tile_expert, tile_start, tile_rows = (empty((max_tiles,), torch.int32, dev) for _ in range(3))
+    n_tiles = empty((1,), torch.int32, dev)
+    lib = _lib("moe.cu")
+    p = _PlanArgs(ids.data_ptr(), order.data_ptr(), tile_expert.data_ptr(), tile_start.data_ptr(), tile_rows.data_ptr(),
+                  n_tiles.data_ptr(), A, E, max_tiles)
+    _check(_launch(lib.gl_moe_plan, byref(p), _stream()), "moe_plan")
+    h = empty((A, F), x.dtype, dev)
+    y = empty((A, hidden), torch.float32, dev)
+    xd, wd = c_int(dtype_code(x.dtype)), c_int(dtype_code(w_gate_up.dtype))
+    g = _ExpertArgs(x.data_ptr(), w_gate_up.data_ptr(), h.data_ptr(), order.data_ptr(), tile_expert.data_ptr(),
+                    tile_start.data_ptr(), tile_rows.data_ptr(), n_tiles.data_ptr(), None, A, F, K, top, max_tiles)
+    _check(_launch(lib.gl_moe_gate_up if USE_MOE_TC else lib.gl_moe_gate_up_simt, byref(g), xd, wd, _stream()), "moe_gate_up")
+    d = _ExpertArgs(h.data_ptr(), w_down.data_ptr(), y.data_ptr(), order.data_ptr(), tile_expert.data_ptr(),
+                    tile_start.data_ptr(), tile_rows.data_ptr(), n_tiles.data_ptr(), weights.data_ptr(), A, hidden, F, top,
+                    max_tiles)
+    _check(_launch(lib.gl_moe_down if USE_MOE_TC else lib.gl_moe_down_simt, byref(d), xd, wd, _stream()), "moe_down")
+    _check(_launch(lib.gl_moe_combine, _ptr(y), _ptr(add), _ptr(out), c_int(T), c_int(hidden), c_int(top), _stream()),
+           "moe_combine")
     return out
 
 

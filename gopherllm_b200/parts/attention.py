@@ -141,7 +141,15 @@ class MixedHeadAttention(Mixer):
     = (q . k) * q_scale; causal softmax per head; with option ``talk`` a learned table M [heads, heads] mixes
     the heads' weights, w_h = sum_g M[h, g] p_g, and head h applies w_h to the values of its own key/value
     head; output projection.  The sum over keys is linear, so the kernel computes every pair (query head's
-    weights, value head) once and mixes the results (csrc/attention_mixed.cu)."""
+    weights, value head) once and mixes the results (csrc/attention_mixed.cu).
+
+    Further options, all off by default.  ``spec.bias``: q, k and v have biases (the output projection has
+    none).  ``q_temp`` = (coef, every): the query at position p is multiplied by
+    1 + coef * ln(floor((p + 1) / every) + 1).  ``score_scale``: the score is (q . k) * score_scale, applied to
+    the 32-bit score (``q_scale`` multiplies q before it is rounded).  ``softcap`` c > 0: score <- c tanh(score / c).
+    ``distance_bias`` x > 0: head h's score loses slope_h * (i - j) for the key at position j <= i, slope_h =
+    2^(-x (h + 1) / heads).  ``shared_kv``: the mixer has no key and value projections; it reads the cache
+    entry another mixer with the same head counts and sizes wrote."""
 
     deferred_add = True
     capturable = True
@@ -161,13 +169,32 @@ class MixedHeadAttention(Mixer):
         self.talk = bool(spec.option("talk", False))
         self.eps = float(spec.option("norm_eps", 1e-6))
         self.position = build_position(spec.position)
-        self.w_qkv = self.w_out = self.q_gamma = self.k_gamma = self.mix = None
+        self.shared_kv = bool(spec.option("shared_kv", False))
+        self.q_temp = spec.option("q_temp", None)
+        self.score_scale = float(spec.option("score_scale", 1.0))
+        self.softcap = float(spec.option("softcap", 0.0) or 0.0)
+        self.distance_bias = float(spec.option("distance_bias", 0.0) or 0.0)
+        if self.q_temp is not None:
+            self.q_temp = (float(self.q_temp[0]), float(self.q_temp[1]))
+            if not self.q_temp[1] > 0:
+                raise ValueError("q_temp: the period must be positive")
+        if self.softcap < 0 or self.distance_bias < 0:
+            raise ValueError("softcap and distance_bias must not be negative")
+        if self.shared_kv and self.row_norm:
+            raise ValueError("a mixer that reads another one's keys has no key norm of its own")
+        self.w_qkv = self.b_qkv = self.w_out = self.q_gamma = self.k_gamma = self.mix = self.slopes = None
 
     def parameters(self) -> Dict[str, ParamSpec]:
         s = self.spec
         q, kv, vv = s.num_heads * s.head_dim, s.num_kv_heads * s.head_dim, s.num_kv_heads * self.vdim
         p = {"q.weight": ParamSpec((q, s.hidden)), "k.weight": ParamSpec((kv, s.hidden)),
              "v.weight": ParamSpec((vv, s.hidden)), "o.weight": ParamSpec((s.hidden, s.num_heads * self.vdim))}
+        if s.bias:
+            p.update({"q.bias": ParamSpec((q,), "vector", "bias"), "k.bias": ParamSpec((kv,), "vector", "bias"),
+                      "v.bias": ParamSpec((vv,), "vector", "bias")})
+        if self.shared_kv:
+            for k in ("k.weight", "v.weight", "k.bias", "v.bias"):
+                p.pop(k, None)
         if self.row_norm:
             p["q_norm.weight"] = ParamSpec((q,), "vector", "gamma")
             p["k_norm.weight"] = ParamSpec((kv,), "vector", "gamma")
@@ -176,13 +203,24 @@ class MixedHeadAttention(Mixer):
         return p
 
     def load(self, t: Dict[str, torch.Tensor]) -> None:
-        ws = [t["q.weight"], t["k.weight"], t["v.weight"]]
+        names = ("q",) if self.shared_kv else ("q", "k", "v")
+        ws = [t[n + ".weight"] for n in names]
         if len({w.dtype for w in ws}) > 1:
             ws = [w.float() for w in ws]
         n = sum(w.shape[0] for w in ws)
-        if n % 8:                                       # output rows of whole 16-byte units
-            ws.append(torch.zeros((8 - n % 8, ws[0].shape[1]), dtype=ws[0].dtype, device=ws[0].device))
+        pad = (8 - n % 8) % 8                           # output rows of whole 16-byte units
+        if pad:
+            ws.append(torch.zeros((pad, ws[0].shape[1]), dtype=ws[0].dtype, device=ws[0].device))
         self.w_qkv = torch.cat(ws, dim=0).contiguous()
+        if self.spec.bias:
+            bs = [t[n + ".bias"].float() for n in names]
+            if pad:
+                bs.append(torch.zeros(pad, dtype=torch.float32, device=bs[0].device))
+            self.b_qkv = torch.cat(bs).contiguous()
+        if self.distance_bias > 0:
+            H = self.spec.num_heads
+            self.slopes = torch.tensor([2.0 ** (-self.distance_bias * (h + 1) / H) for h in range(H)],
+                                       dtype=torch.float64).to(torch.float32).to(self.w_qkv.device)
         self.w_out = t["o.weight"]
         self.q_gamma, self.k_gamma = t.get("q_norm.weight"), t.get("k_norm.weight")
         self.mix = t.get("talk")
@@ -192,19 +230,26 @@ class MixedHeadAttention(Mixer):
         return KVRequest(s.num_kv_heads, s.head_dim, s.window, value_dim=0 if self.vdim == s.head_dim else self.vdim)
 
     def products(self):
-        return [("qkv", self.w_qkv, None, None), ("o", self.w_out, None, None)]
+        return [("qkv", self.w_qkv, self.b_qkv, None), ("o", self.w_out, None, None)]
+
+    def first_product(self):
+        return self.w_qkv, self.b_qkv, None
 
     def until_last(self, xn, ctx, cache, first=None):
         s = self.spec
-        qkv = first if first is not None else ops.linear(xn, self.w_qkv, None, out_dtype=ctx.act_dtype)
+        if self.shared_kv and cache.writes:
+            raise ValueError("a mixer without key and value projections cannot be the writer of its cache entry")
+        qkv = first if first is not None else ops.linear(xn, self.w_qkv, self.b_qkv, out_dtype=ctx.act_dtype)
         tables = self.position.tables(ctx)
         cos, sin = tables if tables is not None else (None, None)
         pages = ctx.pages[cache.group]
         q = ops.qkv_rownorm_to_cache(qkv, cache.k, cache.v, ctx, pages, s.num_heads, s.num_kv_heads, s.head_dim,
                                      self.vdim, s.q_scale, cos, sin, s.position.interleaved,
-                                     self.q_gamma, self.k_gamma, self.eps, write_kv=cache.writes)
+                                     self.q_gamma, self.k_gamma, self.eps, write_kv=cache.writes,
+                                     q_temp=self.q_temp, q_only=self.shared_kv)
         o = ops.attention_mixed(q, cache.k, cache.v, ctx, pages, s.num_heads, s.num_kv_heads, s.head_dim, self.vdim,
-                                mix=self.mix, window=s.window)
+                                mix=self.mix, window=s.window, score_scale=self.score_scale, softcap=self.softcap,
+                                slopes=self.slopes)
         return o, self.w_out, None
 
     def forward(self, xn, ctx, cache, add: Sequence[torch.Tensor], out=None) -> torch.Tensor:

@@ -60,13 +60,13 @@ class AssembledBlock(Block):
 class ParallelBlock(AssembledBlock):
     """x ← (x + ffn(n)) + mixer(n), n = norm(x): one norm feeds both branches
     (model.go:2738-2740) and both are added to the residual, the feed-forward
-    first (model.go:2812-2815)."""
+    first (model.go:2812-2815).  A layer without a feed-forward (``spec.ffn`` None) is x ← x + mixer(n)."""
 
     def _decode_step_as_one_kernel(self, x, ctx, cache) -> bool:
         """With one token a sequence a layer is a stream of weights and cached keys and values; where
         every part offers its fused form and the kernel takes the sizes, the whole block runs as one
         persistent kernel that keeps that stream going from the norm to the residual sum."""
-        if not (ctx.is_decode and ctx.act_dtype == torch.bfloat16 and self.norm.fusable is not None
+        if not (ctx.is_decode and ctx.act_dtype == torch.bfloat16 and self.ffn is not None and self.norm.fusable is not None
                 and self.mixer.decode_fusable is not None and self.ffn.fusable is not None):
             return False
         m = self.mixer.decode_fusable(ctx, cache)
@@ -88,6 +88,9 @@ class ParallelBlock(AssembledBlock):
         if self._decode_step_as_one_kernel(x, ctx, cache):
             return x
         xn = self.norm.forward(x, ctx.act_dtype)
+        if self.ffn is None:
+            self.mixer.forward(xn, ctx, cache, (x,), x)
+            return x
         side = getattr(ctx, "side_stream", None)
         if self.ffn.until_last is not None and self.mixer.until_last is not None:
             # The branches' last products end on the same rows and columns: they run as one product

@@ -108,5 +108,85 @@ class GatedFeedForward(FeedForward):
         return ops.linear(h, w, b, add0=a0, add1=a1, out_dtype=torch.float32, out=out)
 
 
+class MixtureOfExperts(FeedForward):
+    """A mixture of small gated feed-forwards, down(silu(gate(x)) * up(x)) without biases, of which every
+    token uses ``top``.  The router's logits z = W_router x and its scores sigmoid(z) are 32-bit.  The experts
+    form ``groups`` equal groups of neighbours; a group's score is the sum of its two largest scores, and only
+    experts of the best ``keep`` groups can be chosen (one group: every expert can).  The chosen experts'
+    outputs are summed with weights score / (sum of the chosen scores + 1e-20) * ``router_scale``.  A shared
+    expert of the same form (``shared`` > 0: its inner size) runs for every token and is added.
+    Options: ``experts``, ``top``, ``groups``, ``keep``, ``router_scale``, ``shared``; ``intermediate`` is an
+    expert's inner size."""
+    capturable = True
+    launches_only = True
+
+    def __init__(self, spec: FeedForwardSpec):
+        self.spec = spec
+        self.E, self.top = int(spec.option("experts")), int(spec.option("top"))
+        self.groups, self.keep = int(spec.option("groups", 1)), int(spec.option("keep", 1))
+        self.scale = float(spec.option("router_scale", 1.0))
+        self.shared = int(spec.option("shared", 0))
+        if spec.activation != "silu":
+            raise ValueError("the experts' activation is silu")
+        if not (0 < self.top <= self.E and self.groups >= 1 and self.E % self.groups == 0
+                and 1 <= self.keep <= self.groups and self.keep * (self.E // self.groups) >= self.top):
+            raise ValueError(f"moe: top {self.top} of {self.E} experts in {self.groups} groups of which "
+                             f"{self.keep} stay is not possible")
+        self.w_router = self.w_gu = self.w_down = self.ws_gu = self.ws_down = None
+
+    def parameters(self) -> Dict[str, ParamSpec]:
+        s, F = self.spec, self.spec.intermediate
+        p = {"router.weight": ParamSpec((self.E, s.hidden), "vector", "wide")}
+        for e in range(self.E):
+            p[f"e{e}.gate.weight"] = ParamSpec((F, s.hidden))
+            p[f"e{e}.up.weight"] = ParamSpec((F, s.hidden))
+            p[f"e{e}.down.weight"] = ParamSpec((s.hidden, F))
+        if self.shared:
+            p["shared.gate.weight"] = ParamSpec((self.shared, s.hidden))
+            p["shared.up.weight"] = ParamSpec((self.shared, s.hidden))
+            p["shared.down.weight"] = ParamSpec((s.hidden, self.shared))
+        return p
+
+    def load(self, t: Dict[str, torch.Tensor]) -> None:
+        self.w_router = t["router.weight"]
+        mats = [t[f"e{e}.{n}.weight"] for e in range(self.E) for n in ("gate", "up", "down")]
+        if len({m.dtype for m in mats}) > 1:
+            t = dict(t)
+            for k in list(t):
+                if k != "router.weight":
+                    t[k] = t[k].float()
+        # every expert's gate rows, then its up rows: [E, 2F, hidden]; the down weights [E, hidden, F]
+        self.w_gu = torch.stack([torch.cat([t[f"e{e}.gate.weight"], t[f"e{e}.up.weight"]], 0)
+                                 for e in range(self.E)]).contiguous()
+        self.w_down = torch.stack([t[f"e{e}.down.weight"] for e in range(self.E)]).contiguous()
+        if self.shared:
+            self.ws_gu = torch.cat([t["shared.gate.weight"], t["shared.up.weight"]], 0).contiguous()
+            self.ws_down = t["shared.down.weight"]
+
+    def products(self):
+        out = [("router", self.w_router, None, None)]
+        if self.shared:
+            out += [("shared.gate_up", self.ws_gu, None, None), ("shared.down", self.ws_down, None, None)]
+        return out
+
+    def route(self, xn):
+        """(experts int32 [T, top], weights float32 [T, top]) of the step's tokens."""
+        logits = ops.gemm_simt(xn, self.w_router, out_dtype=torch.float32)
+        return ops.moe_route(logits, self.top, self.groups, self.keep, self.scale)
+
+    def forward(self, xn, ctx, add: Sequence[torch.Tensor], out=None) -> torch.Tensor:
+        if len(add) > (2 if self.shared else 1):
+            raise ValueError("more tensors to add than this feed-forward's kernels take")
+        ids, weights = self.route(xn)
+        out = ops.moe_experts(xn, ids, weights, self.w_gu, self.w_down, add=add[0] if len(add) > 0 else None, out=out)
+        if self.shared:
+            gu = ops.linear(xn, self.ws_gu, None, out_dtype=ctx.act_dtype)
+            hs = ops.gated_act(gu, "silu")
+            ops.linear(hs, self.ws_down, None, add0=out, add1=add[1] if len(add) > 1 else None,
+                       out_dtype=torch.float32, out=out)
+        return out
+
+
 register_feed_forward("dense", DenseFeedForward)
+register_feed_forward("moe", MixtureOfExperts)
 register_feed_forward("gated", GatedFeedForward)

@@ -216,6 +216,80 @@ class SelectiveScan(Mixer):
         return _finish(y, w, add, out)
 
 
+class GatedDeltaRule(Mixer):
+    """The gated delta rule: a matrix memory per head that, before it writes, takes back what it already
+    holds under the same key.  q and k have ``num_kv_heads`` heads of ``head_dim`` (each read by
+    heads / kv_heads heads), v has ``num_heads`` heads of ``value_dim``; no biases.  q, k and v each pass a
+    causal convolution per channel (``conv`` taps, the last is the current token's, no bias) and silu; q and k
+    are then brought to unit length, x / sqrt(sum x^2 + 1e-6), q times q_scale.  Per head beta = sigmoid(W_b h)
+    and a decay g = exp(-exp(A_log) softplus(W_a h + dt_bias));
+        S <- g S;  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q.
+    Each head's o is divided by its root mean square (``norm_eps``), times a weight [value_dim] shared by the
+    heads, times silu(W_g h); then the output projection.  The state row holds S [heads, head_dim, value_dim]
+    and the convolution's last taps - 1 inputs.  Options: ``conv``, ``norm_eps``."""
+    capturable = True
+    launches_only = True
+    deferred_add = True
+
+    def __init__(self, spec: MixerSpec):
+        self.spec = spec
+        self.H, self.G = spec.num_heads, spec.num_kv_heads or spec.num_heads
+        self.D, self.V = spec.head_dim, spec.value_dim or spec.head_dim
+        self.taps = int(spec.option("conv", 1))
+        self.eps = float(spec.option("norm_eps", 1e-6))
+        if self.H % self.G:
+            raise ValueError(f"gated_delta: {self.H} heads are not a multiple of {self.G} heads of q and k")
+        if self.taps < 1:
+            raise ValueError("gated_delta: the convolution has at least one tap")
+        self.C = 2 * self.G * self.D + self.H * self.V                  # convolved channels: q, k, v
+        self.tail_off = ops.memory_state_size(ops.MEMORY_DELTA, self.H, self.D, self.V)
+        self.state_size = self.tail_off + self.C * (self.taps - 1)
+        self.w_in = self.conv_w = self.w_o = self.norm = self.a_log = self.dt_bias = None
+
+    def parameters(self) -> Dict[str, ParamSpec]:
+        H, G, D, V, W = self.H, self.G, self.D, self.V, self.spec.hidden
+        return {"q.weight": ParamSpec((G * D, W)), "q.conv": ParamSpec((G * D, self.taps), "vector", "wide"),
+                "k.weight": ParamSpec((G * D, W)), "k.conv": ParamSpec((G * D, self.taps), "vector", "wide"),
+                "v.weight": ParamSpec((H * V, W)), "v.conv": ParamSpec((H * V, self.taps), "vector", "wide"),
+                "b.weight": ParamSpec((H, W)), "a.weight": ParamSpec((H, W)),
+                "A_log": ParamSpec((H,), "vector", "bias"), "dt_bias": ParamSpec((H,), "vector", "wide"),
+                "g.weight": ParamSpec((H * V, W)), "norm.weight": ParamSpec((V,), "vector", "gamma"),
+                "o.weight": ParamSpec((W, H * V))}
+
+    def load(self, t: Dict[str, torch.Tensor]) -> None:
+        names = ("q", "k", "v", "g", "b", "a")
+        self.w_in, _ = _joined([t[n + ".weight"] for n in names], [None] * len(names), t["q.weight"])
+        self.conv_w = torch.cat([t["q.conv"], t["k.conv"], t["v.conv"]], 0).contiguous()
+        self.w_o, self.norm = t["o.weight"], t["norm.weight"]
+        self.a_log, self.dt_bias = t["A_log"], t["dt_bias"]
+        G, D, H, V = self.G, self.D, self.H, self.V
+        self.off = dict(q=0, k=G * D, v=2 * G * D, g=self.C, b=self.C + H * V, a=self.C + H * V + H)
+
+    def cache_request(self):
+        return StateRequest((self.state_size,))
+
+    def first_product(self):
+        return self.w_in, None, None
+
+    def products(self):
+        return [("in", self.w_in, None, None), ("o", self.w_o, None, None)]
+
+    def until_last(self, xn, ctx, cache, first=None):
+        proj = first if first is not None else ops.linear(xn, self.w_in, None, out_dtype=ctx.act_dtype)
+        o = self.off
+        xc = ops.conv_silu(proj, self.conv_w, None, cache.rows, self.tail_off, ctx, x_off=0)
+        mem = ops.memory_scan(ops.MEMORY_DELTA, xc, cache.rows, ctx, self.H, self.D, self.V,
+                              o["q"], o["k"], o["v"], o["b"], o["a"], q_scale=self.spec.q_scale,
+                              gates=proj, a_log=self.a_log, dt_bias=self.dt_bias, kv_heads=self.G)
+        y = ops.head_norm_gate(mem, self.norm, self.H, self.V, self.eps, ctx.act_dtype, gate=proj, gate_off=o["g"],
+                               gate_act="silu")
+        return y, self.w_o, None
+
+    def forward(self, xn, ctx, cache, add: Sequence, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        y, w, _ = self.until_last(xn, ctx, cache)
+        return _finish(y, w, add, out)
+
+
 class NormedPair(Mixer):
     """Two mixers side by side on the same input: each output is RMS-normed over the model width with
     a weight of its own, and the result is ``weight`` times their sum.  The children are whole mixer
@@ -273,3 +347,4 @@ register_mixer("mlstm", MatrixLstm)
 register_mixer("hgrn2", GatedLinearMemory)
 register_mixer("mamba1", SelectiveScan)
 register_mixer("normed_pair", NormedPair)
+register_mixer("gated_delta", GatedDeltaRule)
