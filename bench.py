@@ -4,6 +4,7 @@
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--context 2048] [--layers L]
     python bench.py --model phi-1.5          the same measurements at Phi-1.5's layer sizes
     python bench.py --ragged                 64 unequal prompts as one batch through Model.generate
+    python bench.py --design gozolix         the same for a Gozolix model, beside a Vopedra model of equal width and depth
     python bench.py --design vopedra         prefill and decode of a Vopedra model at a few layer sizes beside a
                                              Phi model of equal width, depth and feed-forward weights
 
@@ -117,7 +118,7 @@ def main():
     ap.add_argument("--sections", default="decode,e2e,prefill,points",
                     help="which measurements to run (for profiling a part): decode,e2e,prefill,points")
     ap.add_argument("--model", default="phi-2", choices=sorted(MODELS), help="whose layer sizes to run")
-    ap.add_argument("--design", default=None, choices=["vopedra"],
+    ap.add_argument("--design", default=None, choices=["vopedra", "gozolix"],
                     help="instead: prefill and decode rates of another design at a few layer sizes, beside the Phi "
                          "model of equal width and depth")
     ap.add_argument("--ragged", action="store_true",
@@ -147,6 +148,8 @@ def main():
 
     if args.design == "vopedra":
         return design_vopedra(args)
+    if args.design == "gozolix":
+        return design_vopedra(args, design="gozolix")
     pk, pk_src = peaks()
     label, sizes, weight_seed = MODELS[args.model]
     cfg = dict(sizes)
@@ -334,9 +337,31 @@ def vopedra_sizes(width, heads, ff, runs_of_loop=2):
             "layers": [mlstm, mamba, pair, mlstm, mamba, pair], "loop": {"start": 1, "stop": 5, "times": runs_of_loop}}
 
 
-def design_vopedra(args):
+def gozolix_sizes(width, heads, ff):
+    """A Gozolix model whose layers resemble a real model's at this width, ten layers: attention with a dense
+    feed-forward, the delta rule with a mixture of 32 experts (4 a token, and a shared one), attention with a
+    dense feed-forward, attention on that layer's keys with a mixture, the delta rule with a dense feed-forward;
+    twice.  A token meets about as many feed-forward weights in every layer as in the other designs."""
+    hd = width // heads
+    attn = {"heads": heads, "kv_heads": max(1, heads // 4), "dim": hd, "vdim": hd, "scale": hd ** -0.5, "softcap": 50.0,
+            "q_temp": {"coef": 0.3, "every": 128}}
+    delta = {"heads": max(1, heads // 4), "kv_heads": max(1, heads // 8), "dim": 2 * hd, "vdim": 4 * hd, "conv": 4}
+    dense = {"kind": "dense", "ff": (3 * ff // 2) // 64 * 64}
+    moe = {"kind": "moe", "expert": {"ff": max(64, ff // 8 // 64 * 64)}, "shared": {"ff": ff // 2 // 64 * 64},
+           "router": {"experts": 32, "top": 4, "scale": 2.5, "groups": {"count": 4, "keep": 2}}}
+    five = [{"type": "attention", "mixer": attn, "mlp": dense}, {"type": "delta", "mixer": delta, "mlp": moe},
+            {"type": "attention", "mixer": attn, "mlp": dense},
+            {"type": "attention", "mixer": dict(attn, kv_from=2), "mlp": moe}, {"type": "delta", "mixer": delta, "mlp": dense}]
+    second = json.loads(json.dumps(five))
+    second[3]["mixer"]["kv_from"] = 7
+    return {"architecture": "Gozolix", "vocab": 32000, "width": width, "norm": {"eps": 1e-6}, "initializer_range": 0.02,
+            "embedding": {"scale": 1.0, "bigram": {"buckets": 65521, "mul_prev": 31, "mul_cur": 7}}, "layers": five + second}
+
+
+def design_vopedra(args, design="vopedra"):
     """Prefill and decode rates of Vopedra models (random weights) beside Phi models of the same width, the
-    same number of layer runs and feed-forwards of the same number of weights.  One JSON line."""
+    same number of layer runs and feed-forwards of the same number of weights; with ``design`` "gozolix", of
+    Gozolix models beside Vopedra models of the same width and number of layer runs.  One JSON line."""
     import numpy as np
     import torch
     import gopherllm_b200 as gl
@@ -397,10 +422,19 @@ def design_vopedra(args):
     clocks.start()
     rows = []
     for width, heads, ff_gated, ff_plain in ((1024, 16, 2752, 4096), (2048, 32, 5504, 8192)):
+        if design == "gozolix":
+            rows.append({"width": width, "heads": heads, "gozolix": measure(gozolix_sizes(width, heads, ff_gated)),
+                         "vopedra": measure(vopedra_sizes(width, heads, ff_gated))})
+            continue
         v = measure(vopedra_sizes(width, heads, ff_gated))
         phi = dict(PHI15, hidden_size=width, num_attention_heads=heads, num_key_value_heads=heads,
                    intermediate_size=ff_plain, vocab_size=32000, num_hidden_layers=v["layer_runs"])
         rows.append({"width": width, "heads": heads, "vopedra": v, "phi": measure(phi)})
+    if design == "gozolix":
+        print(json.dumps({"metric": "prefill and decode rates of Gozolix layer sizes beside Vopedra of equal width and depth (bf16)",
+                          "unit": "tokens/s", "n_gpus": 1, "dtype": "bf16", "data": "synthetic: random weights seed 7, uniform token ids",
+                          "decode_steps_timed": K, "decode_context": 1024, "peaks": pk_src, "clocks": clocks.stop(), "sizes": rows}))
+        return 0
     print(json.dumps({"metric": "prefill and decode rates of Vopedra layer sizes beside Phi of equal width and depth (bf16)",
                       "unit": "tokens/s", "n_gpus": 1, "dtype": "bf16", "data": "synthetic: random weights seed 7, uniform token ids",
                       "decode_steps_timed": K, "decode_context": 1024, "peaks": pk_src, "clocks": clocks.stop(), "sizes": rows}))

@@ -49,15 +49,25 @@ struct GemmArgs {
     const float* biasB;   // [NB] or null
     void* outB;           // [M, NB], the type of out
     int NB, actB;
+    // grouped weights: w holds ``groups`` matrices of N rows one after the other, and every tile of 128 rows
+    // of a multiplies the matrix group_of_tile[row tile] (on the device; a negative entry: the tile is not in
+    // use and is skipped).  Rows sorted by expert and padded to whole tiles per expert make a mixture of
+    // experts one product.  Whole tiles of 128 rows only, tile stores only.
+    const int* group_of_tile;   // [ceil(M / 128)] or null
+    int groups;
 };
 
 // The work of one block: whole output tiles taken round-robin, or (split) an equal share of all
 // (tile, k-block) units in tile order, which cuts tiles where shares meet.  A cut tile is finished by
 // two or more blocks, each adding its part onto the output, so split work needs the add-reduction
 // epilogue and no activation; the part that starts at k-block 0 carries the bias.
+__device__ __forceinline__ void tg_tile_coords(int tile, int tiles_m, int tiles_n_all, int group, int& mt, int& nt);
+
 struct TgWork {
     long long u, end;
     int tile, step, n_tiles, k_blocks, split;
+    const int* in_use = nullptr;      // grouped weights: a row tile with a negative entry is skipped (whole tiles only)
+    int tiles_m = 0, tiles_n_all = 0, group = 1;
     __device__ TgWork(int n_tiles_, int k_blocks_, int split_) : n_tiles(n_tiles_), k_blocks(k_blocks_), split(split_) {
         const long long units = (long long)n_tiles * k_blocks;
         u = units * blockIdx.x / gridDim.x;
@@ -65,8 +75,20 @@ struct TgWork {
         tile = blockIdx.x;
         step = gridDim.x;
     }
+    __device__ void skip_unused(const int* groups_of_tiles, int tiles_m_, int tiles_n_all_, int group_) {
+        in_use = groups_of_tiles; tiles_m = tiles_m_; tiles_n_all = tiles_n_all_; group = group_;
+    }
     __device__ bool next(int& t, int& kb0, int& kb1) {
         if (!split) {
+            if (in_use) {
+                // every role of the block walks the same list, so all of them skip the same tiles
+                while (tile < n_tiles) {
+                    int mt, nt;
+                    tg_tile_coords(tile, tiles_m, tiles_n_all, group, mt, nt);
+                    if (in_use[mt] >= 0) break;
+                    tile += step;
+                }
+            }
             if (tile >= n_tiles) return false;
             t = tile; kb0 = 0; kb1 = k_blocks;
             tile += step;
@@ -154,11 +176,13 @@ gemm_tcgen05_kernel(GemmArgs g, const __grid_constant__ CUtensorMap map_a, const
         if (lane == 0) {
             int it = 0, tile, kb0, kb1;
             TgWork work(n_tiles, k_blocks, split);
+            if (g.group_of_tile) work.skip_unused(g.group_of_tile, tiles_m, tiles_n_all, group);
             while (!failed && work.next(tile, kb0, kb1)) {
                 int mt, nt;
                 tg_tile_coords(tile, tiles_m, tiles_n_all, group, mt, nt);
                 const bool fork = nt >= tiles_n;
                 const int m0 = mt * MT * TG_BM, n0 = (nt - (fork ? tiles_n : 0)) * BN;
+                const int w_row0 = n0 + (g.group_of_tile ? g.group_of_tile[mt] * g.N : 0);
                 for (int kb = kb0; kb < kb1; ++kb, ++it) {
                     const int s = it % STAGES;
                     if (it >= STAGES && !mbar_wait(bar_empty + 8 * s, ((it / STAGES) - 1) & 1)) { failed = 1; break; }
@@ -171,7 +195,7 @@ gemm_tcgen05_kernel(GemmArgs g, const __grid_constant__ CUtensorMap map_a, const
 #pragma unroll
                     for (int i = 0; i < MT; ++i)
                         tma_load_2d(sb + i * TG_BM * 128, ma, k0, m0 + i * TG_BM, bar_full + 8 * s);
-                    tma_load_2d(sb + A_BYTES, mw, k0, n0, bar_full + 8 * s);
+                    tma_load_2d(sb + A_BYTES, mw, k0, w_row0, bar_full + 8 * s);
                 }
             }
         }
@@ -181,6 +205,7 @@ gemm_tcgen05_kernel(GemmArgs g, const __grid_constant__ CUtensorMap map_a, const
             constexpr uint32_t idesc = umma_idesc(BN);
             int it = 0, local = 0, tile, kb0, kb1;
             TgWork work(n_tiles, k_blocks, split);
+            if (g.group_of_tile) work.skip_unused(g.group_of_tile, tiles_m, tiles_n_all, group);
             for (; !failed && work.next(tile, kb0, kb1); ++local) {
                 const int buf = local % NBUF, use = local / NBUF;
                 if (use >= 1 && !mbar_wait(bar_tempty + 8 * buf, (use - 1) & 1)) { failed = 1; break; }
@@ -220,6 +245,7 @@ gemm_tcgen05_kernel(GemmArgs g, const __grid_constant__ CUtensorMap map_a, const
         int local = 0, tile, kb0, kb1;
         TO* O = (TO*)g.out;
         TgWork work(n_tiles, k_blocks, split);
+        if (g.group_of_tile) work.skip_unused(g.group_of_tile, tiles_m, tiles_n_all, group);
         for (; work.next(tile, kb0, kb1); ++local) {
             const int buf = local % NBUF, use = local / NBUF;
             int mt, nt;
@@ -374,7 +400,7 @@ static int launch_tg(const GemmArgs& g, cudaStream_t stream) {
     CUtensorMap map_a, map_w;
     int rc = gl_cached_map_bf16(&map_a, g.a, (uint64_t)g.M, (uint64_t)g.K, TG_BM, TG_BK);
     if (rc != GL_OK) return rc;
-    rc = gl_cached_map_bf16(&map_w, g.w, (uint64_t)g.N, (uint64_t)g.K, BN, TG_BK);
+    rc = gl_cached_map_bf16(&map_w, g.w, (uint64_t)g.N * (g.group_of_tile ? g.groups : 1), (uint64_t)g.K, BN, TG_BK);
     if (rc != GL_OK) return rc;
     CUtensorMap map_a2 = map_a, map_w2 = map_w;
     if (g.a2) {
@@ -396,6 +422,7 @@ static int launch_tg(const GemmArgs& g, cudaStream_t stream) {
         out_mode = 2;
         ga.add0 = nullptr;
     }
+    if (g.group_of_tile && (out_mode != 1 || MT != 1 || g.a2 || g.wB || g.bias)) return GL_ERR_SHAPE;
     if (out_mode != 0) {
         rc = gl_cached_map(&map_out, g.out, (uint64_t)g.M, (uint64_t)g.N, 32, sizeof(TO) == 4 ? 32 : 64, (uint32_t)sizeof(TO));
         if (rc != GL_OK) return rc;
@@ -418,7 +445,7 @@ static int launch_tg(const GemmArgs& g, cudaStream_t stream) {
     const bool can_split = out_mode == 2 && g.act == GL_ACT_NONE && (long long)tiles * k_blocks >= 8LL * sms;
     // (with few rows the tiles are fewer than the SMs: equal shares then whatever the mode when under 70 %
     // of the SMs would have a tile, since part of the machine would otherwise stream all the weights)
-    const int split = can_split && (tg_split_mode > 0 || (tg_split_mode < 0 && uneven && k_blocks >= 64) || tiles * 10 < sms * 7);
+    const int split = !g.group_of_tile && can_split && (tg_split_mode > 0 || (tg_split_mode < 0 && uneven && k_blocks >= 64) || tiles * 10 < sms * 7);
     const int grid = split ? sms : (tiles < sms ? tiles : sms);
     // row tiles of a group: as many as keep the group's activations (all of K) within 28 MB
     const long long a_tile_bytes = (long long)MT * TG_BM * (g.K + (g.a2 ? g.K2 : 0)) * 2;
@@ -466,7 +493,10 @@ GL_API int gl_gemm_tcgen05(const GemmArgs* args, int out_dtype, int bn, cudaStre
         if (g.NB <= 0 || !g.outB || g.a2 || g.add0 || g.add1) return GL_ERR_SHAPE;
         if ((uintptr_t)g.wB & 15) return GL_ERR_ALIGN;
     }
-    if (bn == 0) {
+    if (g.group_of_tile && (g.groups <= 0 || bn > 256)) return GL_ERR_SHAPE;
+    if (bn == 0 && g.group_of_tile) {
+        bn = g.N % 256 == 0 || g.N > 1024 ? 256 : (g.N % 192 == 0 ? 192 : 128);
+    } else if (bn == 0) {
         // A tile's time goes with the operand bytes it pulls from L2, about (128 + width); the
         // grid runs in waves of one tile per SM, and the last wave counts whole.
         static int sms = 0;

@@ -12,6 +12,9 @@
 //   down      for every tile: those rows times the expert's down weights, times the assignment's weight,
 //             written 32-bit at the assignment's own place [token, choice].
 //   combine   out[t] = sum over a token's choices (in the order of the choices) + what is to be added.
+// With many rows an expert (prompts, bfloat16) the plan instead starts every expert's rows on a tile of 128 of
+// their own; the rows are gathered into that order, and gate_up and down are each ONE product with grouped
+// weights on the 5th-generation tensor cores (gemm_tcgen05.cu), with the gated activation between them.
 //
 // A row's result does not depend on which tile it falls in or what else the tile holds: every output
 // element sums over k in ascending order (the 32-bit kernels) or in the tensor cores' fixed order (the
@@ -47,18 +50,7 @@ __device__ __forceinline__ void moe_argmax(const float* sc, int first, int last,
     }
 }
 
-__global__ void __launch_bounds__(128)
-moe_route_kernel(RouteArgs a) {
-    extern __shared__ float smem[];
-    gl_grid_launch_dependents();
-    gl_grid_wait();
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int t = blockIdx.x * 4 + warp;
-    if (t >= a.T) return;
-    float* sc = smem + (size_t)warp * (a.E + a.groups);      // [E] scores, then [groups] group scores
-    float* gsc = sc + a.E;
-    for (int e = lane; e < a.E; e += 32) sc[e] = 1.0f / (1.0f + expf(-a.logits[(size_t)t * a.E + e]));
-    __syncwarp();
+__device__ __forceinline__ void moe_choose(const RouteArgs& a, float* sc, float* gsc, int t, int lane) {
     if (a.groups > 1 && a.keep < a.groups) {
         const int per = a.E / a.groups;
         for (int g = 0; g < a.groups; ++g) {
@@ -108,6 +100,72 @@ moe_route_kernel(RouteArgs a) {
     const float f = a.scale / (sum + 1e-20f);
     __syncwarp();
     for (int k = lane; k < a.top; k += 32) a.weights[(size_t)t * a.top + k] *= f;
+}
+
+__global__ void __launch_bounds__(128)
+moe_route_kernel(RouteArgs a) {
+    extern __shared__ float smem[];
+    gl_grid_launch_dependents();
+    gl_grid_wait();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t = blockIdx.x * 4 + warp;
+    if (t >= a.T) return;
+    float* sc = smem + (size_t)warp * (a.E + a.groups);      // [E] scores, then [groups] group scores
+    float* gsc = sc + a.E;
+    for (int e = lane; e < a.E; e += 32) sc[e] = 1.0f / (1.0f + expf(-a.logits[(size_t)t * a.E + e]));
+    __syncwarp();
+    moe_choose(a, sc, gsc, t, lane);
+}
+
+// The same with the router's product in front: a block a token.  Its four warps take the experts in turn,
+// z_e = sum_k x[k] W[e, k] with the lanes striding over k and a butterfly sum, so a token's logits do not
+// depend on what else is in the step; warp 0 then chooses as the kernel above does.
+struct RouteFromArgs {
+    const void* x;            // [T, K] activation type
+    const float* w;           // [E, K] 32-bit
+    int K;
+    RouteArgs r;              // (logits unused)
+};
+
+template <typename TA>
+__global__ void __launch_bounds__(128)
+moe_route_from_kernel(RouteFromArgs f) {
+    extern __shared__ float smem[];
+    gl_grid_launch_dependents();
+    gl_grid_wait();
+    const RouteArgs& a = f.r;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t = blockIdx.x;
+    float* sc = smem;                        // [E] scores
+    float* gsc = sc + a.E;                   // [groups] group scores
+    float* xs = gsc + a.groups;              // [K] the token's input
+    const TA* x = (const TA*)f.x + (size_t)t * f.K;
+    for (int k = threadIdx.x; k < f.K; k += 128) xs[k] = gl_load(x + k);
+    __syncthreads();
+    for (int e = warp; e < a.E; e += 4) {
+        const float* w = f.w + (size_t)e * f.K;
+        float z = 0.f;
+        for (int k = lane; k < f.K; k += 32) z = fmaf(xs[k], w[k], z);
+        z = gl_warp_sum(z);
+        if (lane == 0) sc[e] = 1.0f / (1.0f + expf(-z));
+    }
+    __syncthreads();
+    if (warp == 0) moe_choose(a, sc, gsc, t, lane);
+}
+
+GL_API int gl_moe_route_from(const RouteFromArgs* args, int x_dtype, cudaStream_t stream) {
+    const RouteFromArgs& f = *args;
+    const RouteArgs& a = f.r;
+    if (a.T <= 0) return GL_OK;
+    if (f.K <= 0 || a.E <= 0 || a.top <= 0 || a.top > a.E || a.groups <= 0 || a.E % a.groups || a.keep <= 0 || a.keep > a.groups) return GL_ERR_SHAPE;
+    if ((long long)a.keep * (a.E / a.groups) < a.top) return GL_ERR_SHAPE;
+    const size_t smem = (size_t)(a.E + a.groups + f.K) * sizeof(float);
+    if (smem > 48 * 1024) return GL_ERR_SMEM;
+    int rc;
+    if (x_dtype == GL_F32) rc = gl_launch(moe_route_from_kernel<float>, dim3(a.T), dim3(128), smem, stream, 1, f);
+    else if (x_dtype == GL_BF16) rc = gl_launch(moe_route_from_kernel<__nv_bfloat16>, dim3(a.T), dim3(128), smem, stream, 1, f);
+    else return GL_ERR_DTYPE;
+    return rc == 0 ? GL_OK : GL_ERR_LAUNCH;
 }
 
 GL_API int gl_moe_route(const RouteArgs* args, cudaStream_t stream) {
@@ -188,6 +246,112 @@ GL_API int gl_moe_plan(const PlanArgs* args, cudaStream_t stream) {
 }
 
 // ---------------------------------------------------------------------------
+// The plan for many rows an expert: every expert's rows start on a tile of ``tile_m`` rows of their own, so that
+// the experts' products are ONE product with grouped weights (a tile of rows meets one expert's matrix).
+// order[row] is the assignment at a padded row (-1: padding), place[assignment] its row, tile_expert[tile] the
+// tile's expert (-1: not in use).
+// ---------------------------------------------------------------------------
+struct PadPlanArgs {
+    const int* ids;           // [A]
+    int* order;               // [max_tiles * tile_m]
+    int* place;               // [A]
+    int* tile_expert;         // [max_tiles]
+    int A, E, max_tiles, tile_m;
+};
+
+__global__ void __launch_bounds__(1024)
+moe_plan_padded_kernel(PadPlanArgs a) {
+    extern __shared__ int ism[];
+    gl_grid_launch_dependents();
+    gl_grid_wait();
+    int* count = ism;                 // [E]
+    int* start = count + a.E;         // [E] the expert's first row, then the running cursor
+    for (int e = threadIdx.x; e < a.E; e += blockDim.x) count[e] = 0;
+    for (int i = threadIdx.x; i < a.max_tiles; i += blockDim.x) a.tile_expert[i] = -1;
+    for (int i = threadIdx.x; i < a.max_tiles * a.tile_m; i += blockDim.x) a.order[i] = -1;
+    __syncthreads();
+    for (int i = threadIdx.x; i < a.A; i += blockDim.x) {
+        int e = a.ids[i];
+        e = e < 0 ? 0 : (e >= a.E ? a.E - 1 : e);
+        atomicAdd(&count[e], 1);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int tiles = 0;
+        for (int e = 0; e < a.E; ++e) {
+            start[e] = tiles * a.tile_m;
+            const int n = (count[e] + a.tile_m - 1) / a.tile_m;
+            for (int i = 0; i < n && tiles + i < a.max_tiles; ++i) a.tile_expert[tiles + i] = e;
+            tiles += n;
+        }
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < a.A; i += blockDim.x) {
+        int e = a.ids[i];
+        e = e < 0 ? 0 : (e >= a.E ? a.E - 1 : e);
+        const int row = atomicAdd(&start[e], 1);
+        if (row < a.max_tiles * a.tile_m) a.order[row] = i;
+        a.place[i] = row;
+    }
+}
+
+GL_API int gl_moe_plan_padded(const PadPlanArgs* args, cudaStream_t stream) {
+    const PadPlanArgs& a = *args;
+    if (a.A <= 0) return GL_OK;
+    if (a.E <= 0 || a.tile_m <= 0 || a.max_tiles < (a.A + a.tile_m - 1) / a.tile_m + (a.E < a.A ? a.E : a.A)) return GL_ERR_SHAPE;
+    const size_t smem = 2 * (size_t)a.E * sizeof(int);
+    if (smem > 48 * 1024) return GL_ERR_SMEM;
+    return gl_launch(moe_plan_padded_kernel, dim3(1), dim3(1024), smem, stream, 1, a) == 0 ? GL_OK : GL_ERR_LAUNCH;
+}
+
+// rows of the padded, sorted input: xs[row] = x[order[row] / top], zeros where order[row] < 0; bfloat16, K % 8 == 0
+__global__ void __launch_bounds__(128)
+moe_gather_rows_kernel(const __nv_bfloat16* x, const int* order, __nv_bfloat16* xs, int K, int top) {
+    gl_grid_launch_dependents();
+    gl_grid_wait();
+    const int row = blockIdx.x;
+    const int src = order[row];
+    uint4* dst = (uint4*)(xs + (size_t)row * K);
+    if (src < 0) {
+        for (int i = threadIdx.x; i < K / 8; i += blockDim.x) dst[i] = make_uint4(0, 0, 0, 0);
+        return;
+    }
+    const uint4* from = (const uint4*)(x + (size_t)(src / top) * K);
+    for (int i = threadIdx.x; i < K / 8; i += blockDim.x) dst[i] = from[i];
+}
+
+GL_API int gl_moe_gather_rows(const void* x, const int* order, void* xs, int rows, int K, int top, cudaStream_t stream) {
+    if (rows <= 0) return GL_OK;
+    if (K <= 0 || K % 8 || top <= 0) return GL_ERR_SHAPE;
+    return gl_launch(moe_gather_rows_kernel, dim3(rows), dim3(128), 0, stream, 1, (const __nv_bfloat16*)x, order,
+                     (__nv_bfloat16*)xs, K, top) == 0 ? GL_OK : GL_ERR_LAUNCH;
+}
+
+// out[t, :] = sum_k weights[t, k] * y[place[t, k], :] (+ add[t, :]), in the order of the choices
+__global__ void __launch_bounds__(256)
+moe_combine_placed_kernel(const float* y, const int* place, const float* weights, const float* add, float* out,
+                          long long n, int N, int top) {
+    gl_grid_launch_dependents();
+    gl_grid_wait();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const long long t = i / N;
+    const int c = (int)(i - t * N);
+    float s = 0.f;
+    for (int k = 0; k < top; ++k) s += weights[t * top + k] * y[(size_t)place[t * top + k] * N + c];
+    out[i] = add ? add[i] + s : s;
+}
+
+GL_API int gl_moe_combine_placed(const float* y, const int* place, const float* weights, const float* add, float* out,
+                                 int T, int N, int top, cudaStream_t stream) {
+    if (T <= 0) return GL_OK;
+    if (N <= 0 || top <= 0) return GL_ERR_SHAPE;
+    const long long n = (long long)T * N;
+    return gl_launch(moe_combine_placed_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, 1, y, place, weights,
+                     add, out, n, N, top) == 0 ? GL_OK : GL_ERR_LAUNCH;
+}
+
+// ---------------------------------------------------------------------------
 // The experts' products, 32-bit FMA on CUDA cores for any element type (the 32-bit path, and what the
 // tensor-core kernels are checked against).  A block: one tile of rows x MOE_TN columns.
 // ---------------------------------------------------------------------------
@@ -202,6 +366,7 @@ struct ExpertArgs {
     const int* n_tiles;
     const float* weights;     // [A] by assignment (down)
     int A, N, K, top, max_tiles;
+    int E;                    // experts (to choose a kernel by the rows an expert meets on average)
 };
 
 #define MOE_TN 64
@@ -414,10 +579,123 @@ moe_expert_tc_kernel(ExpertArgs a) {
             }
 }
 
+// ---------------------------------------------------------------------------
+// Few rows an expert (single tokens of a few sequences): the products are a stream of the chosen experts'
+// weights, every weight row met by one to a few input rows.  A warp owns an output column: its lanes stride
+// over k with 16-byte loads of the weight row (gate and up rows together), the tile's input rows wait in shared
+// memory (eight at a time, 2,048 columns at a time), and a butterfly sum ends each row's dot product.  32-bit
+// accumulation in a fixed order; bfloat16 operands, K a multiple of 8.
+// ---------------------------------------------------------------------------
+#define MV_ROWS 8
+#define MV_KCH 2048
+#define MV_COLS 8
+
+template <bool GATED>
+__global__ void __launch_bounds__(128)
+moe_expert_rows_kernel(ExpertArgs a) {
+    __shared__ __align__(16) __nv_bfloat16 xs[MV_ROWS][MV_KCH];
+    __shared__ int rows[MOE_TM];
+    gl_grid_launch_dependents();
+    gl_grid_wait();
+    const int tile = blockIdx.y;
+    if (tile >= *a.n_tiles) return;
+    const int e = a.tile_expert[tile], start = a.tile_start[tile], nrows = a.tile_rows[tile];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    if (tid < MOE_TM) rows[tid] = tid < nrows ? (GATED ? a.order[start + tid] / a.top : start + tid) : -1;
+    __syncthreads();
+    const __nv_bfloat16* X = (const __nv_bfloat16*)a.x;
+    const __nv_bfloat16* Wg = (const __nv_bfloat16*)a.w + (size_t)e * (GATED ? 2 : 1) * a.N * a.K;
+    const __nv_bfloat16* Wu = Wg + (size_t)a.N * a.K;
+    const int n_first = blockIdx.x * MV_COLS;
+    for (int r0 = 0; r0 < nrows; r0 += MV_ROWS) {
+        const int nr = min(MV_ROWS, nrows - r0);
+        float accg[MV_COLS / 4][MV_ROWS], accu[MV_COLS / 4][MV_ROWS];
+#pragma unroll
+        for (int c = 0; c < MV_COLS / 4; ++c)
+#pragma unroll
+            for (int r = 0; r < MV_ROWS; ++r) accg[c][r] = accu[c][r] = 0.f;
+        for (int k0 = 0; k0 < a.K; k0 += MV_KCH) {
+            const int kn = min(MV_KCH, a.K - k0);
+            __syncthreads();
+            for (int el = tid; el < nr * (kn / 8); el += 128) {
+                const int r = el / (kn / 8), c = (el - r * (kn / 8)) * 8;
+                *(uint4*)&xs[r][c] = *(const uint4*)(X + (size_t)rows[r0 + r] * a.K + k0 + c);
+            }
+            __syncthreads();
+#pragma unroll
+            for (int c = 0; c < MV_COLS / 4; ++c) {
+                const int n = n_first + warp + 4 * c;
+                if (n >= a.N) continue;
+                const __nv_bfloat16* wg = Wg + (size_t)n * a.K + k0;
+                const __nv_bfloat16* wu = Wu + (size_t)n * a.K + k0;
+#pragma unroll 2
+                for (int k = lane * 8; k < kn; k += 256) {
+                    const uint4 rg = *(const uint4*)(wg + k);
+                    uint4 ru = make_uint4(0, 0, 0, 0);
+                    if (GATED) ru = *(const uint4*)(wu + k);
+                    const __nv_bfloat162* pg = (const __nv_bfloat162*)&rg;
+                    const __nv_bfloat162* pu = (const __nv_bfloat162*)&ru;
+                    float g[8], u[8];
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const float2 fg = __bfloat1622float2(pg[i]);
+                        g[2 * i] = fg.x; g[2 * i + 1] = fg.y;
+                        if (GATED) {
+                            const float2 fu = __bfloat1622float2(pu[i]);
+                            u[2 * i] = fu.x; u[2 * i + 1] = fu.y;
+                        }
+                    }
+#pragma unroll
+                    for (int r = 0; r < MV_ROWS; ++r) {
+                        if (r >= nr) break;
+                        const uint4 rx = *(const uint4*)&xs[r][k];
+                        const __nv_bfloat162* px = (const __nv_bfloat162*)&rx;
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            const float2 fx = __bfloat1622float2(px[i]);
+                            accg[c][r] = fmaf(fx.x, g[2 * i], accg[c][r]);
+                            accg[c][r] = fmaf(fx.y, g[2 * i + 1], accg[c][r]);
+                            if (GATED) {
+                                accu[c][r] = fmaf(fx.x, u[2 * i], accu[c][r]);
+                                accu[c][r] = fmaf(fx.y, u[2 * i + 1], accu[c][r]);
+                            }
+                        }
+                    }
+                }
+            }
+        }
+#pragma unroll
+        for (int c = 0; c < MV_COLS / 4; ++c) {
+            const int n = n_first + warp + 4 * c;
+#pragma unroll
+            for (int r = 0; r < MV_ROWS; ++r) {
+                if (r >= nr) break;
+                const float g = gl_warp_sum(accg[c][r]);
+                const float u = GATED ? gl_warp_sum(accu[c][r]) : 0.f;
+                if (lane != 0 || n >= a.N) continue;
+                if (GATED) {
+                    ((__nv_bfloat16*)a.out)[(size_t)(start + r0 + r) * a.N + n] = __float2bfloat16_rn(g / (1.0f + __expf(-g)) * u);
+                } else {
+                    const int asg = a.order[start + r0 + r];
+                    ((float*)a.out)[(size_t)asg * a.N + n] = g * a.weights[asg];
+                }
+            }
+        }
+    }
+}
+
+// how many assignments an expert meets on average before the tiles of rows go to the tensor cores
+#define MV_MAX_ROWS_PER_EXPERT 4
+
 template <bool GATED>
 static int launch_expert(const ExpertArgs& a, int x_dtype, int w_dtype, cudaStream_t stream) {
     if (a.A <= 0 || a.max_tiles <= 0) return GL_OK;
     if (a.N <= 0 || a.K <= 0 || a.top <= 0) return GL_ERR_SHAPE;
+    if (x_dtype == GL_BF16 && w_dtype == GL_BF16 && a.K % 8 == 0 && a.A <= MV_MAX_ROWS_PER_EXPERT * a.E) {
+        const dim3 grid((a.N + MV_COLS - 1) / MV_COLS, a.max_tiles);
+        if (grid.y > 65535) return GL_ERR_SHAPE;
+        return gl_launch(moe_expert_rows_kernel<GATED>, grid, dim3(128), 0, stream, 1, a) == 0 ? GL_OK : GL_ERR_LAUNCH;
+    }
     if (x_dtype == GL_BF16 && w_dtype == GL_BF16 && a.K % 8 == 0) {
         const dim3 grid((a.N + MOE_TN - 1) / MOE_TN, a.max_tiles);
         if (grid.y > 65535) return GL_ERR_SHAPE;

@@ -76,6 +76,7 @@ struct MemoryScanArgs {
     const float* a_log;       // [H]
     const float* dt_bias;     // [H]
     int gates_ld, KVH;        // KVH: heads of q and k (each shared by H / KVH heads of v)
+    int rows_per_thread;      // 0: chosen by the grid's size; else 32, 8, 4, 2 or 1 (for measurements)
 };
 
 // FULL: D == R * DPT and D a multiple of 4, so a thread's rows are DPT consecutive ones read as float4 and no
@@ -332,6 +333,7 @@ static int dispatch_memory_scan(const MemoryScanArgs& a, cudaStream_t stream) {
         pick = dpts[i];                                  // the last that exists if none gives enough blocks
         if (blocks >= want) break;
     }
+    if (a.rows_per_thread > 0 && memory_scan_blocks(a, a.rows_per_thread) > 0) pick = a.rows_per_thread;
     int rc;
     switch (pick) {
         case 32: rc = launch_memory_scan<TA, 32>(a, stream); break;

@@ -798,7 +798,9 @@ class _GemmArgs(Structure):
                 # other kernels' argument structs end before them)
                 ("a2", c_void_p), ("w2", c_void_p), ("bias2", c_void_p), ("K2", c_int),
                 # a second set of columns from the same rows (tcgen05 kernel only)
-                ("wB", c_void_p), ("biasB", c_void_p), ("outB", c_void_p), ("NB", c_int), ("actB", c_int)]
+                ("wB", c_void_p), ("biasB", c_void_p), ("outB", c_void_p), ("NB", c_int), ("actB", c_int),
+                # grouped weights (tcgen05 kernel only): the matrix each tile of 128 rows multiplies
+                ("group_of_tile", c_void_p), ("groups", c_int)]
 
 
 def _gemm_args(a, w, bias, act, add0, add1, out) -> _GemmArgs:
@@ -817,7 +819,7 @@ def _gemm_args(a, w, bias, act, add0, add1, out) -> _GemmArgs:
     if act not in ACTIVATIONS:
         raise KernelError(f"activation {act!r} unknown")
     return _GemmArgs(a.data_ptr(), w.data_ptr(), _addr(bias), _addr(add0), _addr(add1), out.data_ptr(),
-                     M, N, K, ACTIVATIONS[act], None, None, None, 0, None, None, None, 0, 0)
+                     M, N, K, ACTIVATIONS[act], None, None, None, 0, None, None, None, 0, 0, None, 0)
 
 
 def gemm_simt(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None, act=None,
@@ -955,6 +957,27 @@ def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] 
     return out if fork is None else (out, out_b)
 
 
+def gemm_tcgen05_grouped(a: torch.Tensor, w: torch.Tensor, group_of_tile: torch.Tensor, out_dtype: torch.dtype,
+                         tile_n: int = 0) -> torch.Tensor:
+    """out[r] = a[r] . w[g]^T with g = group_of_tile[r // 128]: ``w`` [groups, N, K] holds one matrix per group,
+    every tile of 128 rows of ``a`` [M, K] (M a multiple of 128) multiplies the matrix its entry names, and a
+    tile with a negative entry is skipped (its rows of the result stay as they are).  The table lives on the
+    device: the host need not know it.  bfloat16 operands, K a multiple of 8, N rows of whole 16-byte units."""
+    _need(a, "a", torch.bfloat16)
+    _need(w, "w", torch.bfloat16)
+    _need(group_of_tile, "group_of_tile", torch.int32)
+    M, K = a.shape
+    E, N, Kw = w.shape
+    if Kw != K or K % 8 or M % 128 or group_of_tile.numel() < M // 128 or (N * out_dtype.itemsize) % 16:
+        raise KernelError(f"gemm_tcgen05_grouped: a {tuple(a.shape)}, w {tuple(w.shape)} and {group_of_tile.numel()} tiles do not fit")
+    out = empty((M, N), out_dtype, a.device)
+    g = _GemmArgs(a.data_ptr(), w.data_ptr(), None, None, None, out.data_ptr(), M, N, K, 0,
+                  None, None, None, 0, None, None, None, 0, 0, group_of_tile.data_ptr(), E)
+    fn = _lib("gemm_tcgen05.cu").gl_gemm_tcgen05
+    _check(_launch(fn, byref(g), c_int(dtype_code(out_dtype)), c_int(tile_n), _stream()), "gemm_tcgen05_grouped")
+    return out
+
+
 # ---------------------------------------------------------------------------
 # Mixers with per-sequence state (csrc/recurrent.cu), attention with mixed heads (csrc/attention_mixed.cu)
 class _MemoryScanArgs(Structure):
@@ -963,10 +986,12 @@ class _MemoryScanArgs(Structure):
                 ("ld", c_int), ("q_off", c_int), ("k_off", c_int), ("v_off", c_int), ("i_off", c_int), ("f_off", c_int),
                 ("B", c_int), ("H", c_int), ("D", c_int), ("V", c_int), ("state_stride", c_int), ("kind", c_int),
                 ("cap", c_float), ("q_scale", c_float), ("nm_next", c_void_p),
-                ("gates", c_void_p), ("a_log", c_void_p), ("dt_bias", c_void_p), ("gates_ld", c_int), ("KVH", c_int)]
+                ("gates", c_void_p), ("a_log", c_void_p), ("dt_bias", c_void_p), ("gates_ld", c_int), ("KVH", c_int),
+                ("rows_per_thread", c_int)]
 
 
 MEMORY_GATED, MEMORY_BOUNDED_FORGET, MEMORY_DELTA = 0, 1, 2
+MEMORY_SCAN_ROWS_PER_THREAD = 0     # 0: the kernel chooses by the grid's size; 32, 8, 4, 2 or 1 forces it (measurements)
 
 
 def memory_state_size(kind: int, H: int, D: int, V: int) -> int:
@@ -1039,7 +1064,7 @@ def memory_scan(kind: int, proj: torch.Tensor, state: torch.Tensor, ctx, H: int,
                         ctx.seq_slot.data_ptr(), ctx.seq_qstart.data_ptr(), ctx.seq_qlen.data_ptr(),
                         ld, q_off, k_off, v_off, i_off, f_off, ctx.n_seqs, H, D, V, state.shape[1], kind, cap, q_scale,
                         _addr(nm), _addr(gates), _addr(a_log), _addr(dt_bias),
-                        gates.shape[1] if gates is not None else 0, kv_heads)
+                        gates.shape[1] if gates is not None else 0, kv_heads, MEMORY_SCAN_ROWS_PER_THREAD)
     fn = _lib("recurrent.cu").gl_memory_scan
     _check(_launch(fn, byref(a), c_int(dtype_code(proj.dtype)), _stream()), "memory_scan", 2 if kind == MEMORY_GATED else 1)
     return out
@@ -1319,6 +1344,32 @@ def moe_route(logits: torch.Tensor, top: int, groups: int = 1, keep: int = 1, sc
     return ids, weights
 
 
+class _RouteFromArgs(Structure):
+    _fields_ = [("x", c_void_p), ("w", c_void_p), ("K", c_int), ("r", _RouteArgs)]
+
+
+def moe_route_from(x: torch.Tensor, w_router: torch.Tensor, top: int, groups: int = 1, keep: int = 1, scale: float = 1.0):
+    """``moe_route`` of the logits x . w_router^T ([T, K] in the activation type, [E, K] float32) in one kernel:
+    a token's logits are sums over k in an order of their own, whatever else is in the step.  Inputs too wide
+    for a block's shared memory take the plain product and ``moe_route``."""
+    _need(x, "x")
+    _need(w_router, "w_router", torch.float32)
+    T, K = x.shape
+    E = w_router.shape[0]
+    if w_router.shape[1] != K:
+        raise KernelError(f"moe_route_from: router {tuple(w_router.shape)} does not fit x {tuple(x.shape)}")
+    if (E + groups + K) * 4 > 48 * 1024:
+        return moe_route(gemm_simt(x, w_router, out_dtype=torch.float32), top, groups, keep, scale)
+    if not (0 < top <= E and groups >= 1 and E % groups == 0 and 1 <= keep <= groups and keep * (E // groups) >= top):
+        raise KernelError(f"moe_route: top {top} of {E} experts in {groups} groups of which {keep} stay is not possible")
+    ids = empty((T, top), torch.int32, x.device)
+    weights = empty((T, top), torch.float32, x.device)
+    a = _RouteFromArgs(x.data_ptr(), w_router.data_ptr(), K,
+                       _RouteArgs(None, ids.data_ptr(), weights.data_ptr(), T, E, top, groups, keep, scale))
+    _check(_launch(_lib("moe.cu").gl_moe_route_from, byref(a), c_int(dtype_code(x.dtype)), _stream()), "moe_route")
+    return ids, weights
+
+
 class _PlanArgs(Structure):
     _fields_ = [("ids", c_void_p), ("order", c_void_p), ("tile_expert", c_void_p), ("tile_start", c_void_p),
                 ("tile_rows", c_void_p), ("n_tiles", c_void_p), ("A", c_int), ("E", c_int), ("max_tiles", c_int)]
@@ -1327,9 +1378,16 @@ class _PlanArgs(Structure):
 class _ExpertArgs(Structure):
     _fields_ = [("x", c_void_p), ("w", c_void_p), ("out", c_void_p), ("order", c_void_p), ("tile_expert", c_void_p),
                 ("tile_start", c_void_p), ("tile_rows", c_void_p), ("n_tiles", c_void_p), ("weights", c_void_p),
-                ("A", c_int), ("N", c_int), ("K", c_int), ("top", c_int), ("max_tiles", c_int)]
+                ("A", c_int), ("N", c_int), ("K", c_int), ("top", c_int), ("max_tiles", c_int), ("E", c_int)]
 
 
+class _PadPlanArgs(Structure):
+    _fields_ = [("ids", c_void_p), ("order", c_void_p), ("place", c_void_p), ("tile_expert", c_void_p),
+                ("A", c_int), ("E", c_int), ("max_tiles", c_int), ("tile_m", c_int)]
+
+
+MOE_ROWS_KERNEL_PER_EXPERT = 4     # up to this many (token, choice) pairs an expert on average: the few-rows kernel
+USE_MOE_GROUPED = True             # many rows an expert in bfloat16: one grouped product on tcgen05 (False: tiles on mma.sync)
 USE_MOE_TC = True        # bfloat16 experts on the tensor cores (False: the CUDA-core kernels, for comparison)
 
 
@@ -1358,13 +1416,32 @@ def moe_experts(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, w_gat
         out = empty((T, hidden), torch.float32, x.device)
     _need(out, "out", torch.float32, (T, hidden))
     A = T * top
-    max_tiles = -(-A // MOE_TILE_ROWS) + min(E, A)
     dev = x.device
+    lib = _lib("moe.cu")
+    if (USE_MOE_TC and USE_TCGEN05 and USE_MOE_GROUPED and x.dtype == torch.bfloat16 and w_gate_up.dtype == torch.bfloat16
+            and A > MOE_ROWS_KERNEL_PER_EXPERT * E and K % 8 == 0 and F % 8 == 0 and hidden % 4 == 0):
+        # many rows an expert: rows sorted by expert, every expert on tiles of 128 rows of its own, and each of
+        # the two products one product with grouped weights
+        tiles = -(-A // 128) + min(E, A)
+        order = empty((tiles * 128,), torch.int32, dev)
+        place = empty((A,), torch.int32, dev)
+        tile_expert = empty((tiles,), torch.int32, dev)
+        p = _PadPlanArgs(ids.data_ptr(), order.data_ptr(), place.data_ptr(), tile_expert.data_ptr(), A, E, tiles, 128)
+        _check(_launch(lib.gl_moe_plan_padded, byref(p), _stream()), "moe_plan")
+        xs = empty((tiles * 128, K), torch.bfloat16, dev)
+        _check(_launch(lib.gl_moe_gather_rows, _ptr(x), _ptr(order), _ptr(xs), c_int(tiles * 128), c_int(K), c_int(top),
+                       _stream()), "moe_gather_rows")
+        gu = gemm_tcgen05_grouped(xs, w_gate_up, tile_expert, torch.bfloat16)
+        h = gated_act(gu, "silu")
+        y = gemm_tcgen05_grouped(h, w_down, tile_expert, torch.float32)
+        _check(_launch(lib.gl_moe_combine_placed, _ptr(y), _ptr(place), _ptr(weights), _ptr(add), _ptr(out), c_int(T),
+                       c_int(hidden), c_int(top), _stream()), "moe_combine")
+        return out
+    max_tiles = -(-A // MOE_TILE_ROWS) + min(E, A)
     # (each a tensor of its own: a tape of launches knows temporaries by their first address)
     order = empty((A,), torch.int32, dev)
     tile_expert, tile_start, tile_rows = (empty((max_tiles,), torch.int32, dev) for _ in range(3))
     n_tiles = empty((1,), torch.int32, dev)
-    lib = _lib("moe.cu")
     p = _PlanArgs(ids.data_ptr(), order.data_ptr(), tile_expert.data_ptr(), tile_start.data_ptr(), tile_rows.data_ptr(),
                   n_tiles.data_ptr(), A, E, max_tiles)
     _check(_launch(lib.gl_moe_plan, byref(p), _stream()), "moe_plan")
@@ -1372,11 +1449,11 @@ def moe_experts(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, w_gat
     y = empty((A, hidden), torch.float32, dev)
     xd, wd = c_int(dtype_code(x.dtype)), c_int(dtype_code(w_gate_up.dtype))
     g = _ExpertArgs(x.data_ptr(), w_gate_up.data_ptr(), h.data_ptr(), order.data_ptr(), tile_expert.data_ptr(),
-                    tile_start.data_ptr(), tile_rows.data_ptr(), n_tiles.data_ptr(), None, A, F, K, top, max_tiles)
+                    tile_start.data_ptr(), tile_rows.data_ptr(), n_tiles.data_ptr(), None, A, F, K, top, max_tiles, E)
     _check(_launch(lib.gl_moe_gate_up if USE_MOE_TC else lib.gl_moe_gate_up_simt, byref(g), xd, wd, _stream()), "moe_gate_up")
     d = _ExpertArgs(h.data_ptr(), w_down.data_ptr(), y.data_ptr(), order.data_ptr(), tile_expert.data_ptr(),
                     tile_start.data_ptr(), tile_rows.data_ptr(), n_tiles.data_ptr(), weights.data_ptr(), A, hidden, F, top,
-                    max_tiles)
+                    max_tiles, E)
     _check(_launch(lib.gl_moe_down if USE_MOE_TC else lib.gl_moe_down_simt, byref(d), xd, wd, _stream()), "moe_down")
     _check(_launch(lib.gl_moe_combine, _ptr(y), _ptr(add), _ptr(out), c_int(T), c_int(hidden), c_int(top), _stream()),
            "moe_combine")

@@ -171,8 +171,7 @@ class MixtureOfExperts(FeedForward):
 
     def route(self, xn):
         """(experts int32 [T, top], weights float32 [T, top]) of the step's tokens."""
-        logits = ops.gemm_simt(xn, self.w_router, out_dtype=torch.float32)
-        return ops.moe_route(logits, self.top, self.groups, self.keep, self.scale)
+        return ops.moe_route_from(xn, self.w_router, self.top, self.groups, self.keep, self.scale)
 
     def forward(self, xn, ctx, add: Sequence[torch.Tensor], out=None) -> torch.Tensor:
         if len(add) > (2 if self.shared else 1):

@@ -375,6 +375,16 @@ def test_router_kernel_against_the_plain_router():
         want_order = torch.argsort(chosen, dim=1)
         assert torch.equal(torch.gather(ids.cpu().long(), 1, order), torch.gather(chosen, 1, want_order)), (E, top, groups)
         assert torch.allclose(torch.gather(w.cpu().double(), 1, order), torch.gather(weights, 1, want_order), atol=1e-6)
+    # with the router's product in front, from 32-bit and from bfloat16 inputs
+    for dtype in (torch.float32, torch.bfloat16):
+        x = torch.randn(50, 40, generator=g).to(dtype)
+        wr = torch.randn(12, 40, generator=g)
+        ids, w = ops.moe_route_from(x.cuda(), wr.cuda(), 3, 4, 2, 1.5)
+        chosen, weights = pg.route(x.double(), {"router": wr.double()}, "", {"experts": 12, "top": 3, "scale": 1.5,
+                                                                             "groups": {"count": 4, "keep": 2}})
+        order, want_order = torch.argsort(ids.cpu().long(), dim=1), torch.argsort(chosen, dim=1)
+        assert torch.equal(torch.gather(ids.cpu().long(), 1, order), torch.gather(chosen, 1, want_order))
+        assert torch.allclose(torch.gather(w.cpu().double(), 1, order), torch.gather(weights, 1, want_order), atol=1e-5)
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
@@ -383,13 +393,14 @@ def test_expert_products_with_given_choices(dtype):
     nobody chose, tiles that end ragged, inner sizes that are multiples of nothing; both kernels in bfloat16."""
     from gopherllm_b200 import ops
     g = torch.Generator().manual_seed(5)
-    for T, K, F, N, E, top in ((150, 64, 40, 64, 7, 3), (3, 96, 24, 96, 16, 2), (70, 40, 11, 36, 4, 4), (1, 128, 64, 128, 32, 4)):
+    for T, K, F, N, E, top in ((150, 64, 40, 64, 7, 3), (3, 96, 24, 96, 16, 2), (70, 40, 11, 36, 4, 4), (1, 128, 64, 128, 32, 4),
+                               (20, 72, 24, 40, 16, 2), (2, 2304, 16, 32, 4, 2), (700, 256, 320, 192, 8, 2)):
         x = torch.randn(T, K, generator=g).to(dtype)
         wgu = (torch.randn(E, 2 * F, K, generator=g) / K ** 0.5).to(dtype)
         wd = (torch.randn(E, N, F, generator=g) / F ** 0.5).to(dtype)
         ids = torch.stack([torch.randperm(E, generator=g)[:top] for _ in range(T)]).to(torch.int32)
-        if T > 100:
-            ids[:, 0] = 2                                  # one expert takes every token: several tiles
+        if T in (150, 20):
+            ids[:, 0] = 2                                  # one expert takes every token: several tiles, several chunks of rows
         wts = torch.rand(T, top, generator=g)
         add = torch.randn(T, N, generator=g)
         ref = add.double().clone()
@@ -403,10 +414,13 @@ def test_expert_products_with_given_choices(dtype):
                     h = h.to(torch.bfloat16).double()
                 ref[t] += float(wts[t, k]) * (wd[e].double() @ h)
         tol = 2e-5 if dtype == torch.float32 else 2e-2
-        for tc in ((True, False) if dtype == torch.bfloat16 and K % 8 == 0 else (True,)):
-            ops.USE_MOE_TC = tc
+        # bfloat16: the kernel the sizes choose (few rows an expert, or one grouped product on tcgen05), tiles of
+        # rows on mma.sync, and the CUDA-core kernels
+        for grouped, tc in (((True, True), (False, True), (False, False)) if dtype == torch.bfloat16 else ((True, True),)):
+            ops.USE_MOE_GROUPED, ops.USE_MOE_TC = grouped, tc
             try:
                 out = ops.moe_experts(x.cuda(), ids.cuda(), wts.cuda(), wgu.cuda(), wd.cuda(), add=add.cuda())
             finally:
-                ops.USE_MOE_TC = True
-            assert (out.cpu().double() - ref).abs().max() <= tol * max(1.0, float(ref.abs().max())), (T, K, F, N, E, top, tc)
+                ops.USE_MOE_GROUPED = ops.USE_MOE_TC = True
+            assert (out.cpu().double() - ref).abs().max() <= tol * max(1.0, float(ref.abs().max())), (T, K, F, N, E, top, grouped, tc)
+        ops.check_wait_failures()
