@@ -79,8 +79,8 @@ struct MemoryScanArgs {
     int rows_per_thread;      // 0: chosen by the grid's size; else 32, 8, 4, 2 or 1 (for measurements)
 };
 
-// FULL: D == R * DPT and D a multiple of 4, so a thread's rows are DPT consecutive ones read as float4 and no
-// row needs a bounds check.
+// FULL: D == R * DPT and D a multiple of 4, so a thread's rows are DPT / 4 groups of four consecutive ones read
+// as float4 and no row needs a bounds check.
 template <typename TA, int DPT, int KIND, bool FULL>
 __global__ void __launch_bounds__(MS_THREADS)
 memory_scan_kernel(MemoryScanArgs a, int R, int CH) {
@@ -109,17 +109,81 @@ memory_scan_kernel(MemoryScanArgs a, int R, int CH) {
     float S[DPT], n[DPT];
 #pragma unroll
     for (int i = 0; i < DPT; ++i) {
-        const int d = FULL ? r * DPT + i : r + R * i;
+        const int d = FULL ? ((((i >> 2) * R + r) << 2) + (i & 3)) : r + R * i;
         S[i] = (live && d < D) ? S_g[(size_t)d * V + col] : 0.f;
         n[i] = (KIND == 0 && d < D) ? n_g[d] : 0.f;
     }
     float m = KIND == 0 ? *m_g : 0.f;                 // only thread 0 keeps it current
+    float* out_col = a.out + (size_t)qstart * H * V + (size_t)h * V + (live ? col : 0);
+    float pending = 0.f;                              // kind 2: a token's read-out before its lanes are summed
+
+    // The delta rule's inputs in bfloat16, rows of whole 16-byte units: a chunk's q, k, v and gate inputs are
+    // asked for as 16-byte pieces while the chunk before is still being walked (they wait in registers), so that
+    // a chunk's trip to memory does not stand between two walks.  (Fetched two bytes at a time behind the walk,
+    // the staging of 32 tokens took longer than walking them.)
+    constexpr int PIECES = 3;                         // CH * D <= 5120: at most 640 pieces of 8 for 256 threads
+    const bool fast = KIND == 2 && sizeof(TA) == 2 && (a.ld % 8 == 0) && (a.q_off % 8 == 0) && (a.k_off % 8 == 0) &&
+                      (a.v_off % 8 == 0) && (D % 8 == 0) && (V % 8 == 0) && (((uintptr_t)a.proj & 15) == 0) &&
+                      CH * D <= PIECES * 8 * MS_THREADS;
+    uint4 rq[PIECES], rk[PIECES], rv = make_uint4(0, 0, 0, 0);
+    float rb = 0.f, ra = 0.f;
+    auto fetch = [&](int s0) {
+        const int ns = min(CH, qlen - s0), d8n = D / 8;
+#pragma unroll
+        for (int i = 0; i < PIECES; ++i) {
+            const int e = threadIdx.x + i * MS_THREADS;
+            if (e < ns * d8n) {
+                const int s = e / d8n, d8 = (e - s * d8n) * 8;
+                const TA* row = (const TA*)a.proj + (size_t)(qstart + s0 + s) * a.ld;
+                rq[i] = *(const uint4*)(row + a.q_off + kh * D + d8);
+                rk[i] = *(const uint4*)(row + a.k_off + kh * D + d8);
+            }
+        }
+        const int c8n = CT / 8;
+        if ((int)threadIdx.x < ns * c8n) {
+            const int s = threadIdx.x / c8n, j8 = (threadIdx.x - s * c8n) * 8;
+            const TA* row = (const TA*)a.proj + (size_t)(qstart + s0 + s) * a.ld;
+            rv = col0 + j8 < V ? *(const uint4*)(row + a.v_off + h * V + col0 + j8) : make_uint4(0, 0, 0, 0);
+        }
+        if ((int)threadIdx.x < ns) {
+            const TA* row = (const TA*)a.gates + (size_t)(qstart + s0 + threadIdx.x) * a.gates_ld;
+            rb = gl_load(row + a.i_off + h);
+            ra = gl_load(row + a.f_off + h);
+        }
+    };
+    auto spread = [](const uint4& r, float* dst) {
+        const __nv_bfloat162* p2 = (const __nv_bfloat162*)&r;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float2 f = __bfloat1622float2(p2[i]);
+            dst[2 * i] = f.x;
+            dst[2 * i + 1] = f.y;
+        }
+    };
+    auto stash = [&](int ns) {
+        const int d8n = D / 8, c8n = CT / 8;
+#pragma unroll
+        for (int i = 0; i < PIECES; ++i) {
+            const int e = threadIdx.x + i * MS_THREADS;
+            if (e < ns * d8n) {
+                spread(rq[i], qs + e * 8);
+                spread(rk[i], ks + e * 8);
+            }
+        }
+        if ((int)threadIdx.x < ns * c8n) spread(rv, vs + threadIdx.x * 8);
+        if ((int)threadIdx.x < ns) {
+            gs[threadIdx.x * 4 + 0] = rc_sigmoid(rb);
+            gs[threadIdx.x * 4 + 1] = rc_decay(-expf(a.a_log[h]) * rc_softplus(ra + a.dt_bias[h]));
+        }
+    };
+    if (fast && qlen > 0) fetch(0);
 
     for (int s0 = 0; s0 < qlen; s0 += CH) {
         const int ns = min(CH, qlen - s0);
         __syncthreads();
+        if (fast) stash(ns);
 #pragma unroll 4
-        for (int e = threadIdx.x; e < ns * D; e += MS_THREADS) {
+        for (int e = threadIdx.x; !fast && e < ns * D; e += MS_THREADS) {
             const int s = e / D, d = e - s * D;
             const TA* row = (const TA*)a.proj + (size_t)(qstart + s0 + s) * a.ld;
             const float qp = gl_load(row + a.q_off + kh * D + d);
@@ -135,13 +199,13 @@ memory_scan_kernel(MemoryScanArgs a, int R, int CH) {
                 ks[e] = l + (1.0f - l) * rc_sigmoid(gl_load(row + a.f_off + h * D + d));
             }
         }
-        for (int e = threadIdx.x; e < ns * CT; e += MS_THREADS) {
+        for (int e = threadIdx.x; !fast && e < ns * CT; e += MS_THREADS) {
             const int s = e / CT, j = e - s * CT;
             const TA* row = (const TA*)a.proj + (size_t)(qstart + s0 + s) * a.ld;
             vs[e] = col0 + j < V ? gl_load(row + a.v_off + h * V + col0 + j) : 0.f;
         }
         if (KIND == 2) {
-            if (threadIdx.x < ns) {
+            if (!fast && threadIdx.x < ns) {
                 const TA* row = (const TA*)a.gates + (size_t)(qstart + s0 + threadIdx.x) * a.gates_ld;
                 gs[threadIdx.x * 4 + 0] = rc_sigmoid(gl_load(row + a.i_off + h));
                 gs[threadIdx.x * 4 + 1] = rc_decay(-expf(a.a_log[h]) * rc_softplus(gl_load(row + a.f_off + h) + a.dt_bias[h]));
@@ -160,6 +224,7 @@ memory_scan_kernel(MemoryScanArgs a, int R, int CH) {
                     ks[s * D + d] *= fk;
                 }
             }
+            if (fast && s0 + CH < qlen) fetch(s0 + CH);       // the next chunk's inputs travel while this one is walked
         }
         if (KIND == 0) {
             if (threadIdx.x < ns) {
@@ -198,7 +263,9 @@ memory_scan_kernel(MemoryScanArgs a, int R, int CH) {
             if constexpr (FULL && DPT >= 4) {
 #pragma unroll
                 for (int i = 0; i < DPT; i += 4) {
-                    const float4 q4 = *(const float4*)(q + r * DPT + i), k4 = *(const float4*)(k + r * DPT + i);
+                    // (a thread's rows are groups of four, R groups apart: the lanes of a column read consecutive
+                    // 16-byte pieces, which the banks serve in one go)
+                    const float4 q4 = *(const float4*)(q + (((i >> 2) * R + r) << 2)), k4 = *(const float4*)(k + (((i >> 2) * R + r) << 2));
                     qr[i] = q4.x; qr[i + 1] = q4.y; qr[i + 2] = q4.z; qr[i + 3] = q4.w;
                     kr[i] = k4.x; kr[i + 1] = k4.y; kr[i + 2] = k4.z; kr[i + 3] = k4.w;
                 }
@@ -222,19 +289,37 @@ memory_scan_kernel(MemoryScanArgs a, int R, int CH) {
                 }
             } else if (KIND == 2) {
                 const float beta = gs[s * 4 + 0], decay = gs[s * 4 + 1];
-                float kS = 0.f;
+                // (sums in up to four parts: one chain of DPT dependent multiply-adds would set the token's pace)
+                constexpr int PARTS = DPT >= 4 ? 4 : 1;
+                float part[PARTS];
+#pragma unroll
+                for (int j = 0; j < PARTS; ++j) part[j] = 0.f;
 #pragma unroll
                 for (int i = 0; i < DPT; ++i) {
                     S[i] *= decay;
-                    kS = fmaf(S[i], kr[i], kS);
+                    part[i % PARTS] = fmaf(S[i], kr[i], part[i % PARTS]);
                 }
-                for (int o = R >> 1; o > 0; o >>= 1) kS += __shfl_xor_sync(0xffffffffu, kS, o);
+                float kS = PARTS == 4 ? (part[0] + part[1]) + (part[2] + part[3]) : part[0];
+                // Two sums over a column's lanes a token: S^T k, which the update waits for, and the read-out, which
+                // nothing waits for.  A warp issues in order, so the read-out's butterfly would hold up the next
+                // token; it travels with the next token's first butterfly instead, and is stored a token late.
+                float late = pending;
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) {
+                    const float other = __shfl_xor_sync(0xffffffffu, kS, o);
+                    const float other_late = __shfl_xor_sync(0xffffffffu, late, o);
+                    if (o < R) { kS += other; late += other_late; }
+                }
+                if (s > 0 && r == 0 && live) out_col[(size_t)(s0 + s - 1) * H * V] = late;
                 const float u = beta * (v - kS);
+#pragma unroll
+                for (int j = 0; j < PARTS; ++j) part[j] = 0.f;
 #pragma unroll
                 for (int i = 0; i < DPT; ++i) {
                     S[i] = fmaf(kr[i], u, S[i]);
-                    num = fmaf(S[i], qr[i], num);
+                    part[i % PARTS] = fmaf(S[i], qr[i], part[i % PARTS]);
                 }
+                pending = PARTS == 4 ? (part[0] + part[1]) + (part[2] + part[3]) : part[0];
             } else {
 #pragma unroll
                 for (int i = 0; i < DPT; ++i) {
@@ -243,20 +328,36 @@ memory_scan_kernel(MemoryScanArgs a, int R, int CH) {
                     num = fmaf(S[i], qr[i], num);
                 }
             }
-            for (int o = R >> 1; o > 0; o >>= 1) {
-                num += __shfl_xor_sync(0xffffffffu, num, o);
-                if (KIND == 0) nq += __shfl_xor_sync(0xffffffffu, nq, o);
+            if constexpr (KIND != 2) {
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {                // (R is a power of two; unrolled, the steps beyond it only pass)
+                const float other = __shfl_xor_sync(0xffffffffu, num, o);
+                if (o < R) num += other;
+                if (KIND == 0) {
+                    const float other_n = __shfl_xor_sync(0xffffffffu, nq, o);
+                    if (o < R) nq += other_n;
+                }
             }
             if (r == 0 && live) {
                 float o = num;
                 if (KIND == 0) o = num / (fmaxf(fabsf(nq), es[s]) + 1e-6f);
-                a.out[(size_t)(qstart + s0 + s) * H * V + (size_t)h * V + col] = o;
+                out_col[(size_t)(s0 + s) * H * V] = o;
             }
+            }
+        }
+        if constexpr (KIND == 2) {                        // the chunk's last token's read-out
+            float late = pending;
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                const float other_late = __shfl_xor_sync(0xffffffffu, late, o);
+                if (o < R) late += other_late;
+            }
+            if (r == 0 && live) out_col[(size_t)(s0 + ns - 1) * H * V] = late;
         }
     }
 #pragma unroll
     for (int i = 0; i < DPT; ++i) {
-        const int d = FULL ? r * DPT + i : r + R * i;
+        const int d = FULL ? ((((i >> 2) * R + r) << 2) + (i & 3)) : r + R * i;
         if (d < D) {
             if (live) S_g[(size_t)d * V + col] = S[i];
             if (KIND == 0 && blockIdx.x == 0 && c == 0) a.nm_next[((size_t)b * H + h) * (D + 1) + d] = n[i];
@@ -324,7 +425,9 @@ static int dispatch_memory_scan(const MemoryScanArgs& a, cudaStream_t stream) {
         cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
         if (sms <= 0) sms = 148;
     }
-    const int want = 4 * sms;
+    // (the delta rule's token is a longer chain of dependent steps, which more rows a thread shorten: measured,
+    // a grid of about one block an SM is its best, four an SM the other kinds')
+    const int want = a.kind == 2 ? sms * 85 / 100 : 4 * sms;
     const int dpts[5] = {32, 8, 4, 2, 1};
     int pick = -1;
     for (int i = 0; i < 5; ++i) {

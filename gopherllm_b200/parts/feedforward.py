@@ -132,7 +132,7 @@ class MixtureOfExperts(FeedForward):
                 and 1 <= self.keep <= self.groups and self.keep * (self.E // self.groups) >= self.top):
             raise ValueError(f"moe: top {self.top} of {self.E} experts in {self.groups} groups of which "
                              f"{self.keep} stay is not possible")
-        self.w_router = self.w_gu = self.w_down = self.ws_gu = self.ws_down = None
+        self.w_router = self.w_router_16 = self.w_gu = self.w_down = self.ws_gu = self.ws_down = None
 
     def parameters(self) -> Dict[str, ParamSpec]:
         s, F = self.spec, self.spec.intermediate
@@ -149,6 +149,10 @@ class MixtureOfExperts(FeedForward):
 
     def load(self, t: Dict[str, torch.Tensor]) -> None:
         self.w_router = t["router.weight"]
+        # Router weights whose values bfloat16 holds exactly (a 16-bit checkpoint's are) may go through the
+        # tensor cores: the products are then exact and the sums 32-bit, which is what "32-bit logits" asks for.
+        as16 = self.w_router.to(torch.bfloat16)
+        self.w_router_16 = as16.contiguous() if bool((as16.float() == self.w_router).all()) else None
         mats = [t[f"e{e}.{n}.weight"] for e in range(self.E) for n in ("gate", "up", "down")]
         if len({m.dtype for m in mats}) > 1:
             t = dict(t)
@@ -171,6 +175,9 @@ class MixtureOfExperts(FeedForward):
 
     def route(self, xn):
         """(experts int32 [T, top], weights float32 [T, top]) of the step's tokens."""
+        if xn.dtype == torch.bfloat16 and self.w_router_16 is not None and xn.shape[1] % 8 == 0:
+            logits = ops.linear(xn, self.w_router_16, None, out_dtype=torch.float32)
+            return ops.moe_route(logits, self.top, self.groups, self.keep, self.scale)
         return ops.moe_route_from(xn, self.w_router, self.top, self.groups, self.keep, self.scale)
 
     def forward(self, xn, ctx, add: Sequence[torch.Tensor], out=None) -> torch.Tensor:
