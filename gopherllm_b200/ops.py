@@ -1352,7 +1352,11 @@ def moe_route(logits: torch.Tensor, top: int, groups: int = 1, keep: int = 1, sc
 
 
 class _RouteFromArgs(Structure):
-    _fields_ = [("x", c_void_p), ("w", c_void_p), ("K", c_int), ("r", _RouteArgs)]
+    # (the kernel's record holds the router's record as a member; written out flat here, with the same layout, so
+    # that a tape of launches finds every pointer)
+    _fields_ = [("x", c_void_p), ("w", c_void_p), ("K", c_int),
+                ("logits", c_void_p), ("ids", c_void_p), ("weights", c_void_p),
+                ("T", c_int), ("E", c_int), ("top", c_int), ("groups", c_int), ("keep", c_int), ("scale", c_float)]
 
 
 def moe_route_from(x: torch.Tensor, w_router: torch.Tensor, top: int, groups: int = 1, keep: int = 1, scale: float = 1.0):
@@ -1371,8 +1375,8 @@ def moe_route_from(x: torch.Tensor, w_router: torch.Tensor, top: int, groups: in
         raise KernelError(f"moe_route: top {top} of {E} experts in {groups} groups of which {keep} stay is not possible")
     ids = empty((T, top), torch.int32, x.device)
     weights = empty((T, top), torch.float32, x.device)
-    a = _RouteFromArgs(x.data_ptr(), w_router.data_ptr(), K,
-                       _RouteArgs(None, ids.data_ptr(), weights.data_ptr(), T, E, top, groups, keep, scale))
+    a = _RouteFromArgs(x.data_ptr(), w_router.data_ptr(), K, None, ids.data_ptr(), weights.data_ptr(), T, E, top, groups,
+                       keep, scale)
     _check(_launch(_lib("moe.cu").gl_moe_route_from, byref(a), c_int(dtype_code(x.dtype)), _stream()), "moe_route")
     return ids, weights
 

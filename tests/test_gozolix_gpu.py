@@ -331,6 +331,41 @@ def test_generation_on_the_device_keeps_the_token_before():
     m.close()
 
 
+def test_command_line_generates_and_samples():
+    """python -m gopherllm_b200 on a Gozolix folder: greedy tokens equal the plain implementation's, a sampled
+    run with the sampler's options ends by length, and the isolated kernel bench knows the parts' products."""
+    import os
+    import subprocess
+    import sys
+    cfg = gm.GAMMA
+    folder = folder_for("GAMMA", cfg, 3)
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    run = lambda *a: subprocess.run([sys.executable, "-m", "gopherllm_b200", folder, *a], cwd=root,
+                                    capture_output=True, text=True, timeout=600)
+    prompt = tokens_for(cfg, 9, 77)
+    pcfg, t = gm.read_folder(folder)
+    seq = list(prompt)
+    for _ in range(5):
+        logits = pg.forward(seq, t, pcfg)[-1]
+        top2 = torch.topk(logits, 2).values
+        if float(top2[0] - top2[1]) < 1e-3:
+            break
+        seq.append(int(logits.argmax()))
+    want = seq[len(prompt):]
+    p = run("--prompt", " ".join(map(str, prompt)), "--max-tokens", "5", "--temp", "0", "--repeat-penalty", "1",
+            "--dtype", "float32", "--stop", "100000")
+    assert p.returncode == 0, p.stderr[-2000:]
+    assert [int(x) for x in p.stdout.split()][:len(want)] == want
+    p = run("--prompt", " ".join(map(str, prompt)), "--max-tokens", "12", "--temp", "0.9", "--top-k", "20", "--top-p", "0.95",
+            "--seed", "4", "--stop", "100000")
+    assert p.returncode == 0, p.stderr[-2000:]
+    out = [int(x) for x in p.stdout.split()]
+    assert len(out) == 12 and all(0 <= x < cfg["vocab"] for x in out) and "finish=length" in p.stderr
+    p = run("--kernel-bench-json", "--kernel-bench-runs", "2")
+    assert p.returncode == 0, p.stderr[-2000:]
+    assert json.loads(p.stdout)["kernels"]
+
+
 def test_replay_of_a_trace(tmp_path):
     """The trace runner's loop on a Gozolix model: a batch of two requests, one ends, the other goes on."""
     from gopherllm_b200.engine.replay import run
