@@ -338,11 +338,19 @@ GL_API int gl_qkv_rownorm_cache(const QkvRowNormArgs* args, int act_dtype, int c
     if (a.T <= 0) return GL_OK;
     if (a.hd <= 0 || a.vd <= 0 || a.nH <= 0 || a.nKV <= 0 || 2 * a.half > a.hd) return GL_ERR_SHAPE;
     const size_t smem = (size_t)(a.nH + a.nKV) * a.hd * sizeof(float);
-    if (smem > 48 * 1024) return GL_ERR_SMEM;
+    if (smem > 200 * 1024) return GL_ERR_SMEM;
     // few tokens: more threads a token, so that a row's loads are in flight together
     const dim3 g((unsigned)a.T), b(a.T <= 256 && (a.nH + a.nKV) * a.hd >= 2048 ? 512 : 128);
-    if (act_dtype == GL_F32 && cache_dtype == GL_F32) return gl_launch(qkv_rownorm_cache_kernel<float, float>, g, b, smem, stream, 1, a);
-    if (act_dtype == GL_BF16 && cache_dtype == GL_BF16)
-        return gl_launch(qkv_rownorm_cache_kernel<__nv_bfloat16, __nv_bfloat16>, g, b, smem, stream, 1, a);
-    return GL_ERR_DTYPE;
+    if (act_dtype != cache_dtype || (act_dtype != GL_F32 && act_dtype != GL_BF16)) return GL_ERR_DTYPE;
+    if (smem > 48 * 1024) {                           // (many wide heads: a block may ask for more than the default)
+        const cudaError_t e = act_dtype == GL_F32
+            ? cudaFuncSetAttribute(qkv_rownorm_cache_kernel<float, float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)
+            : cudaFuncSetAttribute(qkv_rownorm_cache_kernel<__nv_bfloat16, __nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) {
+            cudaGetLastError();
+            return GL_ERR_SMEM;
+        }
+    }
+    if (act_dtype == GL_F32) return gl_launch(qkv_rownorm_cache_kernel<float, float>, g, b, smem, stream, 1, a);
+    return gl_launch(qkv_rownorm_cache_kernel<__nv_bfloat16, __nv_bfloat16>, g, b, smem, stream, 1, a);
 }
