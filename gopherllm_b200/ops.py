@@ -1408,7 +1408,11 @@ def moe_experts(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, w_gat
     """out[t] = sum_k weights[t, k] * down_e(silu(gate_e(x[t])) * up_e(x[t])) + add[t], e = ids[t, k]; float32
     [T, hidden].  w_gate_up [E, 2F, K] holds every expert's gate rows and then its up rows, w_down [E, hidden, F].
     The step's (token, choice) pairs are sorted by expert on the device and cut into tiles of rows; the grids
-    cover the most tiles any choice can make, so nothing depends on the host knowing what the router chose."""
+    cover the most tiles any choice can make, so nothing depends on the host knowing what the router chose.
+    Which kernels run depends on the step's size alone: up to MOE_ROWS_KERNEL_PER_EXPERT pairs an expert on
+    average (bfloat16) a weight-streaming kernel, a warp an output column; more (bfloat16): every expert's rows on
+    tiles of 128 of their own and each product one tcgen05 product with grouped weights; other types: tiles of 32
+    rows on the CUDA cores, every sum over k in ascending order."""
     _need(x, "x")
     T, K = x.shape
     _need(ids, "ids", torch.int32)
