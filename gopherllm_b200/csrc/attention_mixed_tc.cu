@@ -65,6 +65,14 @@ __device__ __forceinline__ void ap_mma(float (&d)[4], const unsigned (&a)[4], un
                  : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
+// cap * tanh(x / cap) as cap * (1 - 2 / (e^(2x/cap) + 1)) with the hardware's exponential and reciprocal: off by
+// a few 1e-7 of cap (1e-5 at a cap of 50), which is small against what bfloat16 queries and keys leave in a score
+// (2^-9 of it), and a fifth of the instructions of tanhf; every score of a prompt passes here, and with tanhf the
+// shaping was most of what the kernel issued.  (The 32-bit kernels keep tanhf.)
+__device__ __forceinline__ float ap_softcap(float x, float cap, float two_over_cap) {
+    const float e = __expf(x * two_over_cap);                 // inf for large x: the quotient is then 0
+    return cap * (1.0f - __fdividef(2.0f, e + 1.0f));
+}
 __device__ __forceinline__ unsigned ap_pack(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *(unsigned*)&v;
@@ -131,6 +139,7 @@ attn_pairs_tc_kernel(PairsArgs a) {
     const float LOG2E = 1.4426950408889634f;
     const float slope = a.slopes ? a.slopes[h] : 0.f;
     const bool shaped = a.score_scale != 1.0f || a.softcap > 0.f || a.slopes != nullptr;
+    const float two_over_cap = a.softcap > 0.f ? 2.0f / a.softcap : 0.f;
     const int r_lo = warp * 16 + grp, r_hi = r_lo + 8;        // this thread's two rows inside the tile
     const int pos_lo = p_first + r_lo, pos_hi = p_first + r_hi;
     const int wlo_lo = (a.window > 0 && pos_lo - a.window + 1 > 0) ? pos_lo - a.window + 1 : 0;
@@ -182,7 +191,7 @@ attn_pairs_tc_kernel(PairsArgs a) {
                     for (int e = 0; e < 4; ++e) {
                         const int key = j0 + j * 8 + 2 * t + (e & 1);
                         float x = s[j][e] * a.score_scale;
-                        if (a.softcap > 0.f) x = a.softcap * tanhf(x / a.softcap);
+                        if (a.softcap > 0.f) x = ap_softcap(x, a.softcap, two_over_cap);
                         s[j][e] = x - slope * (float)(((e < 2) ? pos_lo : pos_hi) - key);
                     }
                 }
