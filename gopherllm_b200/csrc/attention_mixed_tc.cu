@@ -43,6 +43,8 @@ struct PairsArgs {
     float score_scale;        // multiplies q . k
     float softcap;            // > 0: s <- softcap * tanh(s / softcap)
     const float* slopes;      // [nH] or null: s <- s - slope_h * (query position - key position)
+    void* out;                // [T, nH*vd] bf16 or null: without a mixing table (nVal 1) the result goes here, rounded,
+                              // and no second kernel has to read the 32-bit pairs again
 };
 
 __device__ __forceinline__ unsigned ap_smem(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
@@ -273,6 +275,20 @@ attn_pairs_tc_kernel(PairsArgs a) {
     const float inv_lo = l_run[0] > 0.f ? 1.f / l_run[0] : 0.f;
     const float inv_hi = l_run[1] > 0.f ? 1.f / l_run[1] : 0.f;
     const int slot = a.nVal > 1 ? vh : 0;
+    if (a.out && a.nVal == 1) {
+        __nv_bfloat16* O = (__nv_bfloat16*)a.out;
+#pragma unroll
+        for (int i = 0; i < AP_NT; ++i) {
+            const int d = i * 8 + 2 * t;
+            if (r_lo < rows)
+                *(__nv_bfloat162*)(O + ((size_t)(qstart + q0 + r_lo) * a.nH + h) * AP_VD + d) =
+                    __floats2bfloat162_rn(o[i][0] * inv_lo, o[i][1] * inv_lo);
+            if (r_hi < rows)
+                *(__nv_bfloat162*)(O + ((size_t)(qstart + q0 + r_hi) * a.nH + h) * AP_VD + d) =
+                    __floats2bfloat162_rn(o[i][2] * inv_hi, o[i][3] * inv_hi);
+        }
+        return;
+    }
 #pragma unroll
     for (int i = 0; i < AP_NT; ++i) {
         const int d = i * 8 + 2 * t;

@@ -1256,7 +1256,8 @@ class _PairsArgs(Structure):
     _fields_ = [("q", c_void_p), ("pairs", c_void_p), ("k_cache", c_void_p), ("v_cache", c_void_p),
                 ("seq_qstart", c_void_p), ("seq_qlen", c_void_p), ("seq_ctx", c_void_p), ("pages", c_void_p),
                 ("B", c_int), ("nH", c_int), ("nKV", c_int), ("nVal", c_int), ("max_pages", c_int), ("window", c_int),
-                ("max_qlen", c_int), ("score_scale", c_float), ("softcap", c_float), ("slopes", c_void_p)]
+                ("max_qlen", c_int), ("score_scale", c_float), ("softcap", c_float), ("slopes", c_void_p),
+                ("out", c_void_p)]
 
 
 USE_PAIRS_TC = True
@@ -1281,8 +1282,19 @@ def attention_mixed(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
     if slopes is not None:
         _need(slopes, "slopes", torch.float32, (num_heads,))
     n_val = num_kv_heads if mix is not None else 1
-    pairs = empty((T, num_heads, n_val, value_dim), torch.float32, q.device)
     out = empty((T, num_heads * value_dim), q.dtype, q.device)
+    pairs_tc = (USE_PAIRS_TC and ctx.max_qlen > 1 and q.dtype == torch.bfloat16 and k_cache.dtype == torch.bfloat16
+                and head_dim % 16 == 0 and value_dim % 16 == 0 and not DEBUG_BOUNDS)
+    if pairs_tc and mix is None:
+        # prompts without a mixing table: the tensor-core kernel rounds and writes the result itself
+        p = _PairsArgs(q.data_ptr(), None, k_cache.data_ptr(), v_cache.data_ptr(),
+                       ctx.seq_qstart.data_ptr(), ctx.seq_qlen.data_ptr(), ctx.seq_ctx.data_ptr(), pages.data_ptr(),
+                       ctx.n_seqs, num_heads, num_kv_heads, 1, pages.shape[-1], window, ctx.max_qlen,
+                       score_scale, softcap, _addr(slopes), out.data_ptr())
+        fn = _lib("attention_mixed_tc.cu", catalog.pair_dim_defines(head_dim, value_dim)).gl_attention_pairs_tc
+        _check(_launch(fn, byref(p), _stream()), "attention_pairs_tc")
+        return out
+    pairs = empty((T, num_heads, n_val, value_dim), torch.float32, q.device)
     a = _MixedAttnArgs(q.data_ptr(), pairs.data_ptr(), out.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), _addr(mix),
                        ctx.seq_qstart.data_ptr(), ctx.seq_qlen.data_ptr(), ctx.seq_ctx.data_ptr(), pages.data_ptr(),
                        T, ctx.n_seqs, num_heads, num_kv_heads, head_dim, value_dim, pages.shape[-1], window,
@@ -1297,12 +1309,11 @@ def attention_mixed(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
         ml = empty((ctx.n_seqs, num_heads, splits, 2), torch.float32, q.device)
         a.parts, a.ml = parts.data_ptr(), ml.data_ptr()
     lib = _lib("attention_mixed.cu")
-    if (USE_PAIRS_TC and ctx.max_qlen > 1 and q.dtype == torch.bfloat16 and k_cache.dtype == torch.bfloat16
-            and head_dim % 16 == 0 and value_dim % 16 == 0 and not DEBUG_BOUNDS):
+    if pairs_tc:
         p = _PairsArgs(q.data_ptr(), pairs.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(),
                        ctx.seq_qstart.data_ptr(), ctx.seq_qlen.data_ptr(), ctx.seq_ctx.data_ptr(), pages.data_ptr(),
                        ctx.n_seqs, num_heads, num_kv_heads, n_val, pages.shape[-1], window, ctx.max_qlen,
-                       score_scale, softcap, _addr(slopes))
+                       score_scale, softcap, _addr(slopes), None)
         fn = _lib("attention_mixed_tc.cu", catalog.pair_dim_defines(head_dim, value_dim)).gl_attention_pairs_tc
         _check(_launch(fn, byref(p), _stream()), "attention_pairs_tc")
         _check(_launch(lib.gl_head_mix, byref(a), c_int(dtype_code(q.dtype)), _stream()), "head_mix")
